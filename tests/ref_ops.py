@@ -59,13 +59,18 @@ def _checked(ids, bound: int, bit: int):
     return ids
 
 
-def embed(ids, table):
-    return _f(table[_checked(ids.long(), table.shape[0], 2)])
+def embed(ids, table, scale=1.0):
+    return _f(table[_checked(ids.long(), table.shape[0], 2)]) * scale
 
 
-def add_rmsnorm(h, delta, w, eps, out_dtype):
+def _normed(delta, gamma, eps):
+    d = _f(delta)
+    return d * torch.rsqrt((d * d).mean(dim=-1, keepdim=True) + eps) * _f(gamma)
+
+
+def add_rmsnorm(h, delta, w, eps, out_dtype, delta_gamma=None, delta_eps=0.0):
     if delta is not None:
-        h += _f(delta)
+        h += _f(delta) if delta_gamma is None else _normed(delta, delta_gamma, delta_eps)
     ms = (h * h).mean(dim=-1, keepdim=True)
     return (h * torch.rsqrt(ms + eps) * _f(w)).to(out_dtype)
 
@@ -213,11 +218,11 @@ def paged_attention(q, step, cache, heads, kv_heads, head_dim, scale, window=Non
     return out
 
 
-def gather_add(h, pending, rows):
+def gather_add(h, pending, rows, pending_gamma=None, pending_eps=0.0):
     r = rows.long()
     out = h[r].clone()
     if pending is not None:
-        out += _f(pending[r])
+        out += _f(pending[r]) if pending_gamma is None else _normed(pending[r], pending_gamma, pending_eps)
     return out
 
 
@@ -270,3 +275,138 @@ def repetition_penalty(logits, tokens, counts, offsets, penalty):
                 v = logits[r, t]
                 logits[r, t] = v / p if v > 0 else (v * p if v < 0 else v)
     return logits
+
+
+# ---- recurrent mixers and what goes with them (the kernels of csrc/causal_conv.cu, selective_scan.cu, min_gru.cu,
+# gated_delta.cu, and the additions to activation.cu and rope_kv.cu)
+def _silu(x):
+    return x * torch.sigmoid(x)
+
+
+def _softplus(x):
+    return torch.where(x > 20, x, torch.log1p(torch.exp(torch.clamp(x, max=20))))
+
+
+def activation(x, kind):
+    v = _f(x)
+    if kind in ("gelu", "gelu_erf"):
+        y = 0.5 * v * (1.0 + torch.erf(v * 0.7071067811865476))
+    elif kind == "gelu_tanh":
+        y = 0.5 * v * (1.0 + torch.tanh(0.7978845608028654 * (v + 0.044715 * v ** 3)))
+    elif kind == "silu":
+        y = _silu(v)
+    elif kind == "relu":
+        y = torch.relu(v)
+    else:
+        raise KeyError(kind)
+    return y.to(x.dtype)
+
+
+def linear_activation(x, w, kind):
+    return activation(linear(x, w), kind)
+
+
+def weighted_sum(a, b, wa, wb):
+    return (wa * _f(a) + wb * _f(b)).to(a.dtype)
+
+
+def _spans(step, state):
+    cu = step.cu_q.tolist()
+    slots = _checked(step.slot_ids.long(), state.shape[0], 8).tolist()
+    return [(cu[s], cu[s + 1], slots[s]) for s in range(step.n_seqs) if cu[s + 1] > cu[s]]
+
+
+def causal_conv(x, taps, bias, state, step, act=True, write_state=True):
+    N, C = x.shape
+    L = taps.shape[1]
+    out = torch.empty((N, C), dtype=x.dtype, device=x.device)
+    for a, b, slot in _spans(step, state):
+        hist = state[slot][:L - 1] if L > 1 else state[slot][:0]
+        full = torch.cat([hist, _f(x[a:b])], dim=0)
+        y = torch.zeros((b - a, C), dtype=torch.float32, device=x.device)
+        for j in range(L):
+            y += full[j:j + (b - a)] * taps[:, j][None, :]
+        if bias is not None:
+            y += bias[None, :]
+        out[a:b] = (_silu(y) if act else y).to(x.dtype)
+        if write_state and L > 1:
+            state[slot][:L - 1] = full[full.shape[0] - (L - 1):]
+    return out
+
+
+def selective_scan(x, proj, z, w_dt, b_dt, a_log, d_skip, state, step, dt_rank, write_state=True):
+    N, I = x.shape
+    S, R = a_log.shape[1], int(dt_rank)
+    p = _f(proj)
+    dt = _softplus(p[:, :R] @ _f(w_dt).T + b_dt)
+    A = -torch.exp(a_log)
+    xs = _f(x)
+    y = torch.empty((N, I), dtype=torch.float32, device=x.device)
+    for a, b, slot in _spans(step, state):
+        h = state[slot].clone()
+        for t in range(a, b):
+            h = torch.exp(dt[t][:, None] * A) * h + (dt[t] * xs[t])[:, None] * p[t, R:R + S][None, :]
+            y[t] = h @ p[t, R + S:R + 2 * S] + d_skip * xs[t]
+        if write_state:
+            state[slot] = h
+    return (y * _silu(_f(z))).to(x.dtype)
+
+
+def min_gru(zxg, b_z, b_x, state, step, write_state=True):
+    N, W = zxg.shape[0], zxg.shape[1] // 3
+    v = _f(zxg)
+    z = torch.sigmoid(v[:, :W] + (b_z if b_z is not None else 0.0))
+    u = v[:, W:2 * W] + (b_x if b_x is not None else 0.0)
+    cand = torch.where(u >= 0, u + 0.5, torch.sigmoid(u))
+    out = torch.empty((N, W), dtype=torch.float32, device=zxg.device)
+    for a, b, slot in _spans(step, state):
+        s = state[slot].clone()
+        for t in range(a, b):
+            s = (1.0 - z[t]) * s + z[t] * cand[t]
+            out[t] = s
+        if write_state:
+            state[slot] = s
+    return (out * _silu(v[:, 2 * W:])).to(zxg.dtype)
+
+
+def gated_delta(qkv, b, a, gate, a_log, dt_bias, norm_w, eps, state, step, heads, kv_heads, dim, vdim, write_state=True,
+                unit_eps=1e-6):
+    N = qkv.shape[0]
+    H, G, D, V = heads, kv_heads, dim, vdim
+    x = _f(qkv)
+    q = x[:, :G * D].reshape(N, G, D)
+    k = x[:, G * D:2 * G * D].reshape(N, G, D)
+    v = x[:, 2 * G * D:].reshape(N, H, V)
+    q = q * torch.rsqrt((q * q).sum(-1, keepdim=True) + unit_eps) * D ** -0.5
+    k = k * torch.rsqrt((k * k).sum(-1, keepdim=True) + unit_eps)
+    beta = torch.sigmoid(_f(b))
+    g = torch.exp(-torch.exp(a_log) * _softplus(_f(a) + dt_bias))
+    rep = H // G
+    o = torch.zeros((N, H, V), dtype=torch.float32, device=qkv.device)
+    for lo, hi, slot in _spans(step, state):
+        S = state[slot].clone()                                  # [H, D, V]
+        for t in range(lo, hi):
+            kt = k[t].repeat_interleave(rep, dim=0)              # [H, D]
+            qt = q[t].repeat_interleave(rep, dim=0)
+            S = g[t][:, None, None] * S
+            u = beta[t][:, None] * (v[t] - torch.einsum("hdv,hd->hv", S, kt))
+            S = S + kt[:, :, None] * u[:, None, :]
+            o[t] = torch.einsum("hdv,hd->hv", S, qt)
+        if write_state:
+            state[slot] = S
+    o = o * torch.rsqrt((o * o).mean(-1, keepdim=True) + eps) * norm_w
+    return (o * _silu(_f(gate)).reshape(N, H, V)).reshape(N, H * V).to(qkv.dtype)
+
+
+def value_norm_pad(qkv, heads, kv_heads, dim, vdim, eps, normed=True):
+    N = qkv.shape[0]
+    H, G, D, Dv = heads, kv_heads, dim, vdim
+    Dp = max(D, Dv)
+    x = _f(qkv)
+    q = x[:, :H * D].reshape(N, H, D)
+    k = x[:, H * D:(H + G) * D].reshape(N, G, D)
+    v = x[:, (H + G) * D:].reshape(N, G, Dv)
+    if normed:
+        v = v * torch.rsqrt((v * v).mean(-1, keepdim=True) + eps)
+    pad = lambda t: torch.nn.functional.pad(t, (0, Dp - t.shape[-1]))
+    return torch.cat([pad(q).reshape(N, -1), pad(k).reshape(N, -1), pad(v).reshape(N, -1)], dim=1).to(qkv.dtype)

@@ -88,6 +88,9 @@ def lookup_architecture(name: str) -> Tuple[type, Callable]:
 
 
 def architecture_name(d: Dict[str, Any], where: str = "config.json") -> str:
+    """The one name under 'architectures' (a list), or the string under 'architecture'."""
+    if d.get("architectures") is None and isinstance(d.get("architecture"), str):
+        return d["architecture"]
     archs = read_key(d, "architectures", list, where=where)
     if len(archs) != 1 or not isinstance(archs[0], str):
         raise ConfigError(f"{where}: 'architectures' should hold exactly one name, got {archs!r}")

@@ -49,3 +49,71 @@ ZAI_API int zai_silu_mul(void* out, const void* gu, int dtype, int N, int F, cud
     const unsigned blocks = (unsigned)((total + threads - 1) / threads);
     ZAI_DISPATCH(dtype, return launch_pdl(silu_mul_kernel<T>, dim3(blocks), dim3(threads), 0, stream, (T*)out, (const T*)gu, F, total));
 }
+
+// ---- an activation on its own:  0 exact (erf) GELU, 1 tanh GELU, 2 SiLU, 3 ReLU; computed in 32-bit
+__device__ __forceinline__ float zai_activate(float v, int kind) {
+    switch (kind) {
+        case 0: return 0.5f * v * (1.f + erff(v * 0.70710678118654752f));
+        case 1: return 0.5f * v * (1.f + tanhf(0.79788456080286536f * (v + 0.044715f * v * v * v)));
+        case 2: return v / (1.f + expf(-v));
+        default: return fmaxf(v, 0.f);
+    }
+}
+
+template <typename T>
+__global__ void activation_kernel(T* __restrict__ out, const T* __restrict__ in, int kind, size_t total) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < total) out[i] = from_float<T>(zai_activate(to_float(in[i]), kind));
+}
+
+__global__ void activation_bf16x8_kernel(bf16* __restrict__ out, const bf16* __restrict__ in, int kind, size_t total8) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total8) return;
+    const uint4 v4 = *reinterpret_cast<const uint4*>(in + i * 8);
+    const __nv_bfloat162* vp = reinterpret_cast<const __nv_bfloat162*>(&v4);
+    uint4 o4;
+    __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&o4);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float2 v = __bfloat1622float2(vp[j]);
+        op[j] = __floats2bfloat162_rn(zai_activate(v.x, kind), zai_activate(v.y, kind));
+    }
+    *reinterpret_cast<uint4*>(out + i * 8) = o4;
+}
+
+ZAI_API int zai_activation(void* out, const void* in, int dtype, int kind, long long total, cudaStream_t stream) {
+    if (total <= 0) return ZAI_OK;
+    if (kind < 0 || kind > 3) return ZAI_BAD_SIZE;
+    const int threads = 256;
+    if (dtype == ZAI_BF16 && (total & 7) == 0 && ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(in)) & 15) == 0) {
+        const size_t total8 = (size_t)total / 8;
+        return launch_pdl(activation_bf16x8_kernel, dim3((unsigned)((total8 + threads - 1) / threads)), dim3(threads), 0, stream,
+                          (bf16*)out, (const bf16*)in, kind, total8);
+    }
+    const unsigned blocks = (unsigned)(((size_t)total + threads - 1) / threads);
+    ZAI_DISPATCH(dtype, return launch_pdl(activation_kernel<T>, dim3(blocks), dim3(threads), 0, stream, (T*)out, (const T*)in, kind,
+                                          (size_t)total));
+}
+
+// ---- out = wa * a + wb * b, in 32-bit, rounded once
+template <typename T>
+__global__ void weighted_sum_kernel(T* __restrict__ out, const T* __restrict__ a, const T* __restrict__ b, float wa, float wb,
+                                    size_t total) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < total) out[i] = from_float<T>(wa * to_float(a[i]) + wb * to_float(b[i]));
+}
+
+ZAI_API int zai_weighted_sum(void* out, const void* a, const void* b, int dtype, float wa, float wb, long long total,
+                             cudaStream_t stream) {
+    if (total <= 0) return ZAI_OK;
+    const int threads = 256;
+    const unsigned blocks = (unsigned)(((size_t)total + threads - 1) / threads);
+    ZAI_DISPATCH(dtype, return launch_pdl(weighted_sum_kernel<T>, dim3(blocks), dim3(threads), 0, stream, (T*)out, (const T*)a,
+                                          (const T*)b, wa, wb, (size_t)total));
+}

@@ -1,0 +1,175 @@
+// Gated delta rule: per head a state matrix S [D, V] in 32-bit, carried between steps.  For each token
+//
+//   S <- g S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q
+//
+// (the read-out sees the token's own write), with q and k unit vectors per head (q also times D^-1/2),
+// beta = sigmoid(b), g = exp(-exp(A_log) softplus(a + dt_bias)).  Three kernels:
+//   * prepare: unit norms, beta and g for every row of the step, all 32-bit;
+//   * the recurrence: the columns of S are independent, so a block owns some columns of one head of one
+//     request and walks the request's rows in order; P lanes of a warp share a column, each with DP of
+//     its D rows in registers; the next token's operands are loaded while the current one is computed;
+//   * the output norm: o / rms(o) * weight * silu(gate) per head, rounded to the model's dtype.
+#include "common.cuh"
+
+__device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log1pf(expf(v)); }
+
+// qk_out [N, 2, G, D]: q then k, unit length (+ eps inside the root), q times D^-1/2;  bg_out [N, 2, H]: beta, g
+template <typename T>
+__global__ void delta_prepare_kernel(float* __restrict__ qk_out, float* __restrict__ bg_out, const T* __restrict__ qkv,
+                                     int qkv_stride, const T* __restrict__ b_in, const T* __restrict__ a_in, int ba_stride,
+                                     const float* __restrict__ a_log, const float* __restrict__ dt_bias, int H, int G, int D,
+                                     float unit_eps) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
+    const float q_scale = rsqrtf((float)D);
+    for (int item = warp; item < 2 * G; item += nwarp) {
+        const T* src = qkv + (size_t)t * qkv_stride + (size_t)item * D;       // q heads, then k heads
+        float ss = 0.f;
+        for (int d = lane; d < D; d += 32) {
+            const float v = to_float(src[d]);
+            ss += v * v;
+        }
+        ss = warp_sum(ss);
+        const float inv = rsqrtf(ss + unit_eps) * (item < G ? q_scale : 1.f);
+        float* dst = qk_out + ((size_t)t * 2 * G + item) * D;
+        for (int d = lane; d < D; d += 32) dst[d] = to_float(src[d]) * inv;
+    }
+    for (int h = threadIdx.x; h < H; h += blockDim.x) {
+        const float b = to_float(b_in[(size_t)t * ba_stride + h]), a = to_float(a_in[(size_t)t * ba_stride + h]);
+        bg_out[(size_t)t * 2 * H + h] = 1.f / (1.f + expf(-b));
+        bg_out[(size_t)t * 2 * H + H + h] = expf(-expf(a_log[h]) * softplus_f(a + dt_bias[h]));
+    }
+}
+
+template <typename T, int DP, int P>
+__global__ void __launch_bounds__(128) gated_delta_kernel(
+    float* __restrict__ o_out, const float* __restrict__ qk, const float* __restrict__ bg, const T* __restrict__ v_in,
+    int v_stride, float* __restrict__ state, const int* __restrict__ cu_q, const int* __restrict__ slot_ids, int H, int G,
+    int D, int V, int write_state, int num_slots, int* __restrict__ status) {
+    pdl_trigger();
+    pdl_wait();
+    constexpr int VB = 128 / P;
+    const int seq = blockIdx.x, h = blockIdx.y, p = threadIdx.x % P;
+    int j = blockIdx.z * VB + threadIdx.x / P;
+    const bool live = j < V;
+    if (!live) j = V - 1;                              // (stays for the shuffles, stores nothing)
+    const int start = cu_q[seq], end = cu_q[seq + 1];
+    if (end <= start) return;
+    const int slot = zai_checked_slot(slot_ids[seq], num_slots, status);
+    const int kvh = h / (H / G), d0 = p * DP;
+    float* st = state + (((size_t)slot * H + h) * D) * V + j;
+    float S[DP], kc[DP], qc[DP], kn[DP], qn[DP];
+#pragma unroll
+    for (int i = 0; i < DP; ++i) S[i] = d0 + i < D ? st[(size_t)(d0 + i) * V] : 0.f;
+    auto load = [&](int t, float (&kk)[DP], float (&qq)[DP], float& beta, float& g, float& vv) {
+        const float* qrow = qk + ((size_t)t * 2 * G + kvh) * D + d0;
+        const float* krow = qk + ((size_t)t * 2 * G + G + kvh) * D + d0;
+#pragma unroll
+        for (int i = 0; i < DP; ++i) {
+            kk[i] = d0 + i < D ? krow[i] : 0.f;
+            qq[i] = d0 + i < D ? qrow[i] : 0.f;
+        }
+        beta = bg[(size_t)t * 2 * H + h];
+        g = bg[(size_t)t * 2 * H + H + h];
+        vv = to_float(v_in[(size_t)t * v_stride + (size_t)h * V + j]);
+    };
+    float beta, g, vv, beta_n = 0.f, g_n = 0.f, vv_n = 0.f;
+    load(start, kc, qc, beta, g, vv);
+    for (int t = start; t < end; ++t) {
+        if (t + 1 < end) load(t + 1, kn, qn, beta_n, g_n, vv_n);
+        float dot = 0.f;
+#pragma unroll
+        for (int i = 0; i < DP; ++i) {
+            S[i] *= g;
+            dot += S[i] * kc[i];
+        }
+#pragma unroll
+        for (int o = P / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        const float u = beta * (vv - dot);
+        float out = 0.f;
+#pragma unroll
+        for (int i = 0; i < DP; ++i) {
+            S[i] += kc[i] * u;
+            out += S[i] * qc[i];
+        }
+#pragma unroll
+        for (int o = P / 2; o > 0; o >>= 1) out += __shfl_xor_sync(0xffffffffu, out, o);
+        if (p == 0 && live) o_out[(size_t)t * H * V + (size_t)h * V + j] = out;
+#pragma unroll
+        for (int i = 0; i < DP; ++i) {
+            kc[i] = kn[i];
+            qc[i] = qn[i];
+        }
+        beta = beta_n; g = g_n; vv = vv_n;
+    }
+    if (write_state && live) {
+#pragma unroll
+        for (int i = 0; i < DP; ++i)
+            if (d0 + i < D) st[(size_t)(d0 + i) * V] = S[i];
+    }
+}
+
+// out[t, h, :] = o[t, h, :] * rsqrt(mean(o^2) + eps) * w * silu(gate[t, h, :]); one warp per (row, head)
+template <typename T>
+__global__ void gated_rmsnorm_kernel(T* __restrict__ out, const float* __restrict__ o, const float* __restrict__ w,
+                                     const T* __restrict__ gate, int gate_stride, float eps, int items, int H, int V) {
+    pdl_trigger();
+    pdl_wait();
+    const int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (item >= items) return;
+    const int t = item / H, h = item % H;
+    const float* src = o + (size_t)item * V;
+    float ss = 0.f;
+    for (int d = lane; d < V; d += 32) ss += src[d] * src[d];
+    ss = warp_sum(ss);
+    const float inv = rsqrtf(ss / (float)V + eps);
+    const T* grow = gate + (size_t)t * gate_stride + (size_t)h * V;
+    for (int d = lane; d < V; d += 32) {
+        const float gv = to_float(grow[d]);
+        out[(size_t)item * V + d] = from_float<T>(src[d] * inv * (w ? w[d] : 1.f) * (gv / (1.f + expf(-gv))));
+    }
+}
+
+ZAI_API int zai_delta_prepare(float* qk_out, float* bg_out, const void* qkv, int qkv_stride, const void* b_in, const void* a_in,
+                              int ba_stride, int dtype, const float* a_log, const float* dt_bias, int N, int H, int G, int D,
+                              float unit_eps, cudaStream_t stream) {
+    if (N <= 0) return ZAI_OK;
+    ZAI_DISPATCH(dtype, return launch_pdl(delta_prepare_kernel<T>, dim3(N), dim3(128), 0, stream, qk_out, bg_out, (const T*)qkv,
+        qkv_stride, (const T*)b_in, (const T*)a_in, ba_stride, a_log, dt_bias, H, G, D, unit_eps));
+}
+
+template <typename T, int DP, int P>
+static int launch_delta(float* o_out, const float* qk, const float* bg, const void* v_in, int v_stride, float* state,
+                        const int* cu_q, const int* slot_ids, int n_seqs, int H, int G, int D, int V, int write_state,
+                        int num_slots, int* status, cudaStream_t stream) {
+    const int vb = 128 / P;
+    return launch_pdl(gated_delta_kernel<T, DP, P>, dim3(n_seqs, H, (V + vb - 1) / vb), dim3(128), 0, stream, o_out, qk, bg,
+                      (const T*)v_in, v_stride, state, cu_q, slot_ids, H, G, D, V, write_state, num_slots, status);
+}
+
+// o_out [N, H*V] 32-bit; qk, bg from zai_delta_prepare; v_in [N, v_stride] (heads of V values); state [slots, H, D, V]
+ZAI_API int zai_gated_delta(float* o_out, const float* qk, const float* bg, const void* v_in, int v_stride, int dtype,
+                            float* state, const int* cu_q, const int* slot_ids, int N, int n_seqs, int H, int G, int D, int V,
+                            int write_state, int num_slots, int* status, cudaStream_t stream) {
+    if (N <= 0 || n_seqs <= 0) return ZAI_OK;
+    if (D < 1 || D > 256 || V < 1 || G < 1 || H % G != 0 || H > 65535 || V > 65535 * 16) return ZAI_BAD_SIZE;
+#define ZAI_DELTA(DPV, PV) ZAI_DISPATCH(dtype, return launch_delta<T, DPV, PV>(o_out, qk, bg, v_in, v_stride, state, cu_q, slot_ids, \
+        n_seqs, H, G, D, V, write_state, num_slots, status, stream))
+    if (D <= 16) ZAI_DELTA(4, 4);
+    if (D <= 32) ZAI_DELTA(8, 4);
+    if (D <= 64) ZAI_DELTA(16, 4);
+    if (D <= 128) ZAI_DELTA(32, 4);
+    ZAI_DELTA(32, 8);
+#undef ZAI_DELTA
+}
+
+ZAI_API int zai_gated_rmsnorm(void* out, const float* o, const float* w, const void* gate, int gate_stride, int dtype, float eps,
+                              int N, int H, int V, cudaStream_t stream) {
+    const long long items = (long long)N * H;
+    if (items <= 0) return ZAI_OK;
+    const long long blocks = (items + 3) / 4;
+    if (blocks > 0x7fffffffLL) return ZAI_BAD_SIZE;
+    ZAI_DISPATCH(dtype, return launch_pdl(gated_rmsnorm_kernel<T>, dim3((unsigned)blocks), dim3(128), 0, stream, (T*)out, o, w,
+        (const T*)gate, gate_stride, eps, (int)items, H, V));
+}

@@ -92,6 +92,44 @@ __global__ void __launch_bounds__(256) add_rmsnorm_vec_kernel(float* __restrict_
     }
 }
 
+// The same with a pending term that passes a norm of its own before it is added (a block with a norm
+// after each sublayer):  h += delta * rsqrt(mean(delta^2) + eps_d) * gamma_d;  out = rms(h) * gamma.
+template <typename T>
+__global__ void add_normed_rmsnorm_kernel(float* __restrict__ h, const T* __restrict__ delta, const float* __restrict__ gamma_d,
+                                          float eps_d, const float* __restrict__ gamma, T* __restrict__ out, float eps, int H) {
+    __shared__ float red[33];
+    pdl_trigger();
+    pdl_wait();
+    const size_t base = (size_t)blockIdx.x * H;
+    float sd = 0.f;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        const float d = to_float(delta[base + c]);
+        sd += d * d;
+    }
+    sd = block_sum(sd, red);
+    const float inv_d = rsqrtf(sd / (float)H + eps_d);
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        const float v = h[base + c] + to_float(delta[base + c]) * inv_d * gamma_d[c];
+        h[base + c] = v;
+        ss += v * v;
+    }
+    if (!out) return;
+    ss = block_sum(ss, red);
+    const float inv = rsqrtf(ss / (float)H + eps);
+    for (int c = threadIdx.x; c < H; c += blockDim.x)
+        out[base + c] = from_float<T>(h[base + c] * inv * gamma[c]);
+}
+
+// `out` (and `gamma`) may be null: then only the residual stream is updated.
+ZAI_API int zai_add_normed_rmsnorm(float* h, const void* delta, const float* gamma_d, float eps_d, const float* gamma, void* out,
+                                   int dtype, float eps, int N, int H, cudaStream_t stream) {
+    if (N <= 0) return ZAI_OK;
+    const int threads = H >= 2048 ? 512 : 256;
+    ZAI_DISPATCH(dtype, return launch_pdl(add_normed_rmsnorm_kernel<T>, dim3(N), dim3(threads), 0, stream, h, (const T*)delta,
+                                          gamma_d, eps_d, gamma, (T*)out, eps, H));
+}
+
 ZAI_API int zai_add_rmsnorm(float* h, const void* delta, const float* gamma, void* out, int dtype, float eps,
                             int N, int H, cudaStream_t stream) {
     if (N <= 0) return ZAI_OK;

@@ -401,3 +401,53 @@ ZAI_API int zai_kv_write(const void* k, int k_stride, const void* v, int v_strid
         (const T*)k, k_stride, (const T*)v, v_stride, positions, seq_idx, block_table, table_width, (T*)pages,
         page_size, Hkv, D, num_pages, status));
 }
+
+// ---- between the projection and the kernels above, for attention whose values pass an RMS norm (no weight)
+// before they are cached, and whose value heads may differ in size from the query/key heads:
+//   in  [N, Hq*D + Hkv*D + Hkv*Dv]            out [N, (Hq + 2 Hkv) * Dp],  Dp = max(D, Dv)
+// q and k heads are copied and filled with zeros up to Dp (zeros change no score), v heads are divided
+// by their root mean square over Dv and filled with zeros likewise.  With D == Dv and out == in only
+// the v heads are touched.  One warp per (row, head); the norm is 32-bit.
+template <typename T>
+__global__ void value_norm_pad_kernel(T* __restrict__ out, const T* __restrict__ in, int in_stride, int Hq, int Hkv, int D,
+                                      int Dv, int Dp, float eps, int normed, long long items) {
+    pdl_trigger();
+    pdl_wait();
+    const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (item >= items) return;
+    const int n_heads = Hq + 2 * Hkv;
+    const bool in_place = (const T*)out == in;
+    const int heads_here = in_place ? Hkv : n_heads;
+    const long long t = item / heads_here;
+    const int h = in_place ? Hq + Hkv + (int)(item % heads_here) : (int)(item % heads_here);
+    const bool is_v = h >= Hq + Hkv;
+    const T* src = in + (size_t)t * in_stride + (is_v ? (size_t)(Hq + Hkv) * D + (size_t)(h - Hq - Hkv) * Dv : (size_t)h * D);
+    T* dst = out + ((size_t)t * n_heads + h) * Dp;
+    const int n = is_v ? Dv : D;
+    float inv = 1.f;
+    if (is_v && normed) {
+        float ss = 0.f;
+        for (int d = lane; d < n; d += 32) {
+            const float v = to_float(src[d]);
+            ss += v * v;
+        }
+        ss = warp_sum(ss);
+        inv = rsqrtf(ss / (float)n + eps);
+    } else if (in_place) {
+        return;
+    }
+    for (int d = lane; d < Dp; d += 32) dst[d] = d < n ? from_float<T>(to_float(src[d]) * inv) : from_float<T>(0.f);
+}
+
+ZAI_API int zai_value_norm_pad(void* out, const void* in, int in_stride, int dtype, int N, int Hq, int Hkv, int D, int Dv,
+                               float eps, int normed, cudaStream_t stream) {
+    if (N <= 0) return ZAI_OK;
+    const int Dp = D > Dv ? D : Dv;
+    if (out == in && D != Dv) return ZAI_BAD_SIZE;
+    const long long items = (long long)N * (out == in ? Hkv : Hq + 2 * Hkv);
+    const long long blocks = (items + 3) / 4;
+    if (blocks > 0x7fffffffLL) return ZAI_BAD_SIZE;
+    ZAI_DISPATCH(dtype, return launch_pdl(value_norm_pad_kernel<T>, dim3((unsigned)blocks), dim3(128), 0, stream, (T*)out,
+                                          (const T*)in, in_stride, Hq, Hkv, D, Dv, Dp, eps, normed, items));
+}

@@ -21,7 +21,7 @@ def main(argv=None) -> int:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens live requests hold at any time (each rounded up to 64)")
     ap.add_argument("--page-size", type=int, default=64)
-    ap.add_argument("--max-requests", type=int, default=8)
+    ap.add_argument("--max-requests", type=int, default=4, help="state slots: the most requests live at any time")
     ap.add_argument("--stats", default=None, metavar="FILE",
                     help="when the input ends, write the cache's and the runner's counters to FILE as JSON")
     args = ap.parse_args(argv)

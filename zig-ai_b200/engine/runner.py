@@ -225,15 +225,17 @@ def load_runner(model_dir: str, dtype="bfloat16", max_tokens: int = 4096, max_re
     from ..config import load_config
     from ..weights import load_tensors
     tdtype = parse_dtype(dtype)
+    cfg = load_config(model_dir)
+    model = build_model(cfg)
     if ops is None:
         from ..kernels import ops as cuda_ops
         ops = cuda_ops
-        ops.require(tdtype)
+        # the libraries every model uses, and those its parts name: compiled together at the first call
+        extra = sorted({lib for part in model.all_parts() for lib in getattr(part, "kernel_libs", ())})
+        ops.require(tdtype, extra)
     if device is None:
         device = torch.device("cuda", torch.cuda.current_device()) if ops.device_type == "cuda" else torch.device("cpu")
     device = torch.device(device)
-    cfg = load_config(model_dir)
-    model = build_model(cfg)
     tensors = load_tensors(model_dir, model.param_decls(), tdtype, device, unexpected=unexpected_tensors)
     model.bind(tensors, tdtype)
     num_pages = max(-(-int(max_tokens) // page_size), 1)

@@ -26,17 +26,31 @@ _P, _I, _F = c_void_p, c_int, c_float
 
 _SIGNATURES = {
     "embed": {
-        "zai_embed": [_P, _P, _I, _P, _I, _I, _I, _P, _P],
+        "zai_embed": [_P, _P, _I, _P, _I, _I, _I, _F, _P, _P],
         "zai_gather_add": [_P, _P, _P, _I, _P, _I, _I, _P],
+        "zai_gather_add_normed": [_P, _P, _P, _I, _P, _F, _P, _I, _I, _P],
     },
-    "norm": {"zai_add_rmsnorm": [_P, _P, _P, _P, _I, _F, _I, _I, _P]},
-    "activation": {"zai_silu_mul": [_P, _P, _I, _I, _I, _P]},
+    "norm": {"zai_add_rmsnorm": [_P, _P, _P, _P, _I, _F, _I, _I, _P],
+             "zai_add_normed_rmsnorm": [_P, _P, _P, _F, _P, _P, _I, _F, _I, _I, _P]},
+    "activation": {"zai_silu_mul": [_P, _P, _I, _I, _I, _P],
+                   "zai_activation": [_P, _P, _I, _I, ctypes.c_longlong, _P],
+                   "zai_weighted_sum": [_P, _P, _P, _I, _F, _F, ctypes.c_longlong, _P]},
+    "causal_conv": {"zai_causal_conv": [_P, _I, _P, _I, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P]},
+    "selective_scan": {"zai_selective_scan": [_P, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I,
+                                              _I, _P, _P]},
+    "min_gru": {"zai_min_gru": [_P, _P, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P]},
+    "gated_delta": {
+        "zai_delta_prepare": [_P, _P, _P, _I, _P, _P, _I, _I, _P, _P, _I, _I, _I, _I, _F, _P],
+        "zai_gated_delta": [_P, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+        "zai_gated_rmsnorm": [_P, _P, _P, _P, _I, _I, _F, _I, _I, _I, _P],
+    },
     "shortconv": {"zai_short_conv": [_P, _P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P]},
     "rope_kv": {
         "zai_rope_table": [_P, _P, _P, _I, _I, _P],
         "zai_qk_norm_rope": [_P, _I, _I, _P, _P, _F, _P, _I, _P, _P, _P, _I, _P, _I, _P, _P,
                              _I, _I, _I, _I, _I, _I, _I, _P, _P],
         "zai_kv_write": [_P, _I, _P, _I, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _P, _P],
+        "zai_value_norm_pad": [_P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
     },
     "attention": {
         "zai_paged_attention_general": [_P, _P, _P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P, _P],
@@ -128,13 +142,14 @@ CORE_LIBS = ("embed", "norm", "activation", "shortconv", "rope_kv", "attention",
 BF16_LIBS = ("attention_mma", "attention_tma", "attention_tc", "decode_gemm")
 
 
-def require(dtype=None) -> None:
+def require(dtype=None, extra=()) -> None:
     """Fail loudly unless a CUDA device is present and the libraries load that a model of `dtype`
     uses (all of them if no dtype is given).  What is missing or out of date is compiled now, several
-    sources at a time; a library outside this set is compiled when it is first called."""
+    sources at a time; a library outside this set is compiled when it is first called.  `extra`:
+    further libraries that the model's parts name (`kernel_libs`)."""
     if not torch.cuda.is_available():
         raise KernelError("no CUDA device: this engine has no CPU path")
-    libs = list(CORE_LIBS)
+    libs = list(CORE_LIBS) + [x for x in extra if x not in CORE_LIBS]
     if dtype is None or dtype == torch.bfloat16:
         libs += list(BF16_LIBS)
         if dtype is None or USE_TC_GEMM:
@@ -303,20 +318,26 @@ _EPI_BF16, _EPI_F32, _EPI_SWIGLU = 0, 1, 2
 
 
 @_timed("embedding")
-def embed(ids, table):
+def embed(ids, table, scale=1.0):
+    """Rows of the table as 32-bit residual rows, times `scale`."""
     _cuda(ids, table)
     N, (V, H) = ids.numel(), table.shape
     out = torch.empty((N, H), dtype=torch.float32, device=table.device)
-    _check(_fn("embed", "zai_embed")(_ptr(out), _ptr(table), _dt(table), _ptr(ids), N, H, V, _status_ptr(table.device),
-                                     _stream()), "embed")
+    _check(_fn("embed", "zai_embed")(_ptr(out), _ptr(table), _dt(table), _ptr(ids), N, H, V, float(scale),
+                                     _status_ptr(table.device), _stream()), "embed")
     return out
 
 
 @_timed("norm")
-def gather_add(h, pending, rows):
-    _cuda(h, pending, rows)
+def gather_add(h, pending, rows, pending_gamma=None, pending_eps=0.0):
+    """h[rows] + pending[rows]; with `pending_gamma` the pending rows pass an RMS norm with that weight first."""
+    _cuda(h, pending, rows, pending_gamma)
     R, H = rows.numel(), h.shape[1]
     out = torch.empty((R, H), dtype=torch.float32, device=h.device)
+    if pending_gamma is not None:
+        _check(_fn("embed", "zai_gather_add_normed")(_ptr(out), _ptr(h), _ptr(pending), _dt(pending), _ptr(pending_gamma),
+                                                     float(pending_eps), _ptr(rows), R, H, _stream()), "gather_add_normed")
+        return out
     pd = _dt(pending) if pending is not None else _F32
     _check(_fn("embed", "zai_gather_add")(_ptr(out), _ptr(h), _ptr(pending), pd, _ptr(rows), R, H, _stream()),
            "gather_add")
@@ -324,14 +345,20 @@ def gather_add(h, pending, rows):
 
 
 @_timed("norm")
-def add_rmsnorm(h, delta, w, eps, out_dtype):
-    _cuda(h, delta, w)
+def add_rmsnorm(h, delta, w, eps, out_dtype, delta_gamma=None, delta_eps=0.0):
+    """h += delta (in place, 32-bit), then the RMS norm of h with weight w.  With `delta_gamma` the pending
+    term passes an RMS norm of its own (that weight, `delta_eps`) before it is added."""
+    _cuda(h, delta, w, delta_gamma)
     if h.dtype != torch.float32 or w.dtype != torch.float32:
         raise KernelError("the residual stream and norm weights are 32-bit")
     N, H = h.shape
     out = torch.empty((N, H), dtype=out_dtype, device=h.device)
     if delta is not None and delta.dtype != out_dtype:
         raise KernelError("the pending term should have the model's dtype")
+    if delta_gamma is not None:
+        _check(_fn("norm", "zai_add_normed_rmsnorm")(_ptr(h), _ptr(delta), _ptr(delta_gamma), float(delta_eps), _ptr(w), _ptr(out),
+                                                     _dt(out), float(eps), N, H, _stream()), "add_normed_rmsnorm")
+        return out
     _check(_fn("norm", "zai_add_rmsnorm")(_ptr(h), _ptr(delta), _ptr(w), _ptr(out), _dt(out), float(eps), N, H,
                                           _stream()), "add_rmsnorm")
     return out
@@ -896,4 +923,151 @@ def sample(logits, temperature, top_k, top_p, u, with_status=False):
     out = torch.empty((R + (1 if with_status else 0),), dtype=torch.int32, device=logits.device)
     _check(_fn("sampling", "zai_sample")(_ptr(out), _ptr(logits), _ptr(temperature), _ptr(top_k), _ptr(top_p),
                                          _ptr(u), R, V, _status_ptr(logits.device) if with_status else None, _stream()), "sample")
+    return out
+
+
+# ----------------------------------------------------------------------------- recurrent mixers and what goes with them
+ACTIVATIONS = {"gelu": 0, "gelu_erf": 0, "gelu_tanh": 1, "silu": 2, "relu": 3}
+
+
+@_timed("activation")
+def activation(x, kind):
+    """An activation by name (gelu / gelu_erf, gelu_tanh, silu, relu), computed in 32-bit."""
+    _cuda(x)
+    out = torch.empty_like(x)
+    _check(_fn("activation", "zai_activation")(_ptr(out), _ptr(x), _dt(x), ACTIVATIONS[kind], x.numel(), _stream()), "activation")
+    return out
+
+
+def linear_activation(x, w, kind):
+    """act(x . w^T): the product (x may be a LazyNorm), then the activation."""
+    return activation(linear(x, w), kind)
+
+
+@_timed("activation")
+def weighted_sum(a, b, wa, wb):
+    """wa * a + wb * b, in 32-bit, rounded once."""
+    _cuda(a, b)
+    if a.shape != b.shape or a.dtype != b.dtype:
+        raise KernelError("the two terms should have one shape and dtype")
+    out = torch.empty_like(a)
+    _check(_fn("activation", "zai_weighted_sum")(_ptr(out), _ptr(a), _ptr(b), _dt(a), float(wa), float(wb), a.numel(), _stream()),
+           "weighted_sum")
+    return out
+
+
+def _rows_view(x):
+    """(pointer, row stride) of a 2-D tensor whose rows are contiguous (a column slice of a wider matrix)."""
+    if x.dim() != 2 or x.stride(1) != 1 or not x.is_cuda:
+        raise KernelError("kernels take CUDA matrices with contiguous rows")
+    return x.data_ptr(), x.stride(0)
+
+
+@_timed("conv")
+def causal_conv(x, taps, bias, state, step, act=True, write_state=True):
+    """Causal depthwise convolution over time of x [N, C] (a column slice is fine) with taps [C, L], the
+    request's last L-1 inputs in `state` [slots, L-1, C] (32-bit), an optional bias and SiLU."""
+    _cuda(taps, bias, state)
+    xp, xs = _rows_view(x)
+    N, C = x.shape
+    L = taps.shape[1]
+    if state.dtype != torch.float32 or state.shape[-1] != C or (L > 1 and state.shape[1] != L - 1):
+        raise KernelError("the conv state is 32-bit [slots, taps - 1, channels]")
+    out = torch.empty((N, C), dtype=x.dtype, device=x.device)
+    single = bool(step.decode_only and N == step.n_seqs)
+    _check(_fn("causal_conv", "zai_causal_conv")(
+        _ptr(out), C, xp, xs, _dt(x), _ptr(taps), _ptr(bias), _ptr(state), _ptr(step.seq_idx), _ptr(step.cu_q),
+        _ptr(step.slot_ids), N, step.n_seqs, C, L, int(bool(act)), int(single), int(bool(write_state)), state.shape[0],
+        _status_ptr(x.device), _stream()), "causal_conv", 1 if (single or not write_state or L == 1) else 2)
+    return out
+
+
+@_timed("recurrence")
+def selective_scan(x, proj, z, w_dt, b_dt, a_log, d_skip, state, step, dt_rank, write_state=True):
+    """The selective-scan recurrence: x [N, I] (after its convolution), proj [N, R + 2S] = (dt_in | B | C), z [N, I]
+    (a column slice is fine), w_dt [I, R], b_dt [I], a_log [I, S], d_skip [I], state [slots, I, S] 32-bit.
+    Returns (scan + d_skip * x) * silu(z) in x's dtype."""
+    _cuda(x, w_dt, b_dt, a_log, d_skip, state)
+    N, I = x.shape
+    S, R = a_log.shape[1], int(dt_rank)
+    pp, ps = _rows_view(proj)
+    zp, zs = _rows_view(z)
+    if proj.shape[1] < R + 2 * S or w_dt.dtype != x.dtype or proj.dtype != x.dtype or z.dtype != x.dtype:
+        raise KernelError("selective_scan: operands do not fit together")
+    if state.dtype != torch.float32 or tuple(state.shape[1:]) != (I, S):
+        raise KernelError("the scan state is 32-bit [slots, inner, state]")
+    y = torch.empty((N, I), dtype=x.dtype, device=x.device)
+    _check(_fn("selective_scan", "zai_selective_scan")(
+        _ptr(y), _ptr(x), pp, ps, zp, zs, _dt(x), _ptr(w_dt), _ptr(b_dt), _ptr(a_log), _ptr(d_skip), _ptr(state),
+        _ptr(step.cu_q), _ptr(step.slot_ids), N, step.n_seqs, I, S, R, int(bool(write_state)), state.shape[0],
+        _status_ptr(x.device), _stream()), "selective_scan")
+    return y
+
+
+@_timed("recurrence")
+def min_gru(zxg, b_z, b_x, state, step, write_state=True):
+    """The minimal gated recurrence over zxg [N, 3W] = (gate | candidate | output gate) with the state [slots, W]
+    in 32-bit; returns state * silu(output gate) per row, [N, W]."""
+    _cuda(b_z, b_x, state)
+    p, stride = _rows_view(zxg)
+    N, W = zxg.shape[0], zxg.shape[1] // 3
+    if state.dtype != torch.float32 or tuple(state.shape[1:]) != (W,):
+        raise KernelError("the recurrence's state is 32-bit [slots, width]")
+    out = torch.empty((N, W), dtype=zxg.dtype, device=zxg.device)
+    _check(_fn("min_gru", "zai_min_gru")(_ptr(out), p, stride, _dt(zxg), _ptr(b_z), _ptr(b_x), _ptr(state), _ptr(step.cu_q),
+                                         _ptr(step.slot_ids), N, step.n_seqs, W, int(bool(write_state)), state.shape[0],
+                                         _status_ptr(zxg.device), _stream()), "min_gru")
+    return out
+
+
+@_timed("recurrence")
+def gated_delta(qkv, b, a, gate, a_log, dt_bias, norm_w, eps, state, step, heads, kv_heads, dim, vdim, write_state=True,
+                unit_eps=1e-6):
+    """The gated delta rule over the rows of a step.  qkv [N, 2 G D + H V] (q heads, k heads, v heads, after their
+    convolutions), b and a [N, H], gate [N, H V] (column slices are fine), state [slots, H, D, V] 32-bit.
+    Returns rms(o) * norm_w * silu(gate) per head, [N, H V] in qkv's dtype."""
+    _cuda(a_log, dt_bias, norm_w, state)
+    N = qkv.shape[0]
+    H, G, D, V = int(heads), int(kv_heads), int(dim), int(vdim)
+    qp, qs = _rows_view(qkv)
+    bp, bs = _rows_view(b)
+    ap, as_ = _rows_view(a)
+    gp, gs = _rows_view(gate)
+    if bs != as_ or state.dtype != torch.float32 or tuple(state.shape[1:]) != (H, D, V):
+        raise KernelError("gated_delta: operands do not fit together")
+    dev = qkv.device
+    qk = torch.empty((N, 2, G, D), dtype=torch.float32, device=dev)
+    bg = torch.empty((N, 2, H), dtype=torch.float32, device=dev)
+    o = torch.empty((N, H * V), dtype=torch.float32, device=dev)
+    out = torch.empty((N, H * V), dtype=qkv.dtype, device=dev)
+    lib = "gated_delta"
+    _check(_fn(lib, "zai_delta_prepare")(_ptr(qk), _ptr(bg), qp, qs, bp, ap, bs, _dt(qkv), _ptr(a_log), _ptr(dt_bias), N, H, G, D,
+                                         float(unit_eps), _stream()), "delta_prepare")
+    vp = qp + 2 * G * D * qkv.element_size()
+    _check(_fn(lib, "zai_gated_delta")(_ptr(o), _ptr(qk), _ptr(bg), vp, qs, _dt(qkv), _ptr(state), _ptr(step.cu_q),
+                                       _ptr(step.slot_ids), N, step.n_seqs, H, G, D, V, int(bool(write_state)), state.shape[0],
+                                       _status_ptr(dev), _stream()), "gated_delta")
+    _check(_fn(lib, "zai_gated_rmsnorm")(_ptr(out), _ptr(o), _ptr(norm_w), gp, gs, _dt(qkv), float(eps), N, H, V, _stream()),
+           "gated_rmsnorm")
+    return out
+
+
+@_timed("q/k norm, rotation, page write")
+def value_norm_pad(qkv, heads, kv_heads, dim, vdim, eps, normed=True):
+    """Prepares projection rows [N, H D + G D + G Dv] for the attention kernels: value heads divided by their root
+    mean square over Dv (no weight) if `normed`, and, where D != Dv, every head filled with zeros up to max(D, Dv).
+    Works in place where no head changes its size."""
+    _cuda(qkv)
+    N = qkv.shape[0]
+    H, G, D, Dv = int(heads), int(kv_heads), int(dim), int(vdim)
+    if qkv.shape[1] != H * D + G * D + G * Dv:
+        raise KernelError("value_norm_pad: the rows do not hold q, k and v heads of these sizes")
+    if D == Dv:
+        if not normed:
+            return qkv
+        out = qkv
+    else:
+        out = torch.empty((N, (H + 2 * G) * max(D, Dv)), dtype=qkv.dtype, device=qkv.device)
+    _check(_fn("rope_kv", "zai_value_norm_pad")(_ptr(out), _ptr(qkv), qkv.shape[1], _dt(qkv), N, H, G, D, Dv, float(eps),
+                                                int(bool(normed)), _stream()), "value_norm_pad")
     return out

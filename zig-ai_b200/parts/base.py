@@ -135,6 +135,15 @@ class Residual:
         self.data = data
 
 
+class NormedTerm:
+    """A pending term that passes an RMS norm of its own (weight `gamma`, `eps`) before it is added to
+    the residual stream: what a block with a norm after each sublayer hands to the next norm, so that
+    the norm behind a sublayer, the residual addition and the norm before the next sublayer are one kernel."""
+
+    def __init__(self, data, gamma, eps: float):
+        self.data, self.gamma, self.eps = data, gamma, float(eps)
+
+
 class LazyNorm:
     """A norm that has not run yet: `norm(residual + delta) * gamma`, optionally on gathered rows.
     A product kernel that can apply it on the fly takes it as its input (`ops.linear`,

@@ -9,7 +9,7 @@ pending term into the next norm's kernel, which adds it into the 32-bit residual
 """
 from __future__ import annotations
 
-from .base import Block, register_part
+from .base import Block, NormedTerm, register_part
 
 
 class PreNormResidual(Block):
@@ -33,4 +33,40 @@ class PreNormResidual(Block):
         return h, f
 
 
+class SandwichResidual(Block):
+    """A norm before and a norm after each sublayer; the feed-forward is optional:
+
+        h = h + post_mixer(mixer(pre_mixer(h)));   h = h + post_ff(feed_forward(pre_ff(h)))
+
+    The norm after a sublayer, the addition and the norm before the next sublayer run as one kernel: a
+    sublayer's output travels as a `NormedTerm` into the next norm (of this block, of the next block, or
+    the model's final norm)."""
+    graph_safe = True      # forward launches kernels only; nothing is read back to the host
+
+    def __init__(self, mixer, mixer_norm, mixer_post_norm, feed_forward=None, ff_norm=None, ff_post_norm=None):
+        super().__init__()
+        self.mixer_norm = self.sub("mixer_norm", "norm", mixer_norm)
+        self.mixer = self.sub("mixer", "mixer", mixer)
+        self.mixer_post_norm = self.sub("mixer_post_norm", "norm", mixer_post_norm)
+        self.feed_forward = None
+        if feed_forward is not None:
+            self.ff_norm = self.sub("ff_norm", "norm", ff_norm)
+            self.feed_forward = self.sub("feed_forward", "feed_forward", feed_forward)
+            self.ff_post_norm = self.sub("ff_post_norm", "norm", ff_post_norm)
+
+    def params(self):
+        return {}
+
+    def forward(self, h, pending, step, cache, write_cache=True):
+        r = self.mixer_norm.forward(h, pending, step, lazy=self.mixer.accepts_lazy_input)
+        m = self.mixer.forward(r, step, self.cache_for(self.mixer, cache), write_cache)
+        term = NormedTerm(m, self.mixer_post_norm.weight, self.mixer_post_norm.eps)
+        if self.feed_forward is None:
+            return h, term
+        r2 = self.ff_norm.forward(h, term, step, lazy=self.feed_forward.accepts_lazy_input)
+        f = self.feed_forward.forward(r2, step)
+        return h, NormedTerm(f, self.ff_post_norm.weight, self.ff_post_norm.eps)
+
+
 register_part("block", "prenorm_residual", PreNormResidual)
+register_part("block", "sandwich_residual", SandwichResidual)

@@ -15,8 +15,9 @@ from .base import Embedding, Head, ParamDecl, register_part
 class TokenEmbedding(Embedding):
     graph_safe = True      # forward launches kernels only; nothing is read back to the host
 
-    def __init__(self, weight: str, vocab: int, hidden: int):
+    def __init__(self, weight: str, vocab: int, hidden: int, scale: float = 1.0):
         self.weight_name, self.vocab, self.hidden = weight, int(vocab), int(hidden)
+        self.scale = float(scale)          # the gathered rows are multiplied by it (in 32-bit)
         self.table = None
 
     def params(self):
@@ -26,6 +27,8 @@ class TokenEmbedding(Embedding):
         self.table = tensors[self.weight_name]
 
     def forward(self, token_ids, step):
+        if self.scale != 1.0:
+            return step.ops.embed(token_ids, self.table, self.scale)
         return step.ops.embed(token_ids, self.table)
 
 

@@ -35,4 +35,30 @@ class SwiGlu(FeedForward):
         return ops.linear(a, self.w_down)
 
 
+class DenseMlp(FeedForward):
+    """`down( act(up(x)) )`, no gate and no biases; `activation` is one of gelu (the exact one, with erf),
+    gelu_tanh, silu, relu.  `names` gives the two tensors' names."""
+    accepts_lazy_input = True     # x goes straight into a product
+    graph_safe = True
+
+    def __init__(self, hidden: int, ff_dim: int, activation: str = "gelu", names=None):
+        self.hidden, self.ff_dim, self.activation = int(hidden), int(ff_dim), str(activation)
+        if self.activation not in ("gelu", "gelu_erf", "gelu_tanh", "silu", "relu"):
+            raise ValueError(f"unknown activation '{self.activation}'")
+        self.names = {"up": "ffn_up.weight", "down": "ffn_down.weight", **(names or {})}
+
+    def params(self):
+        return {self.names["up"]: ParamDecl((self.ff_dim, self.hidden)),
+                self.names["down"]: ParamDecl((self.hidden, self.ff_dim))}
+
+    def bind(self, tensors, dtype):
+        self.w_up, self.w_down = tensors[self.names["up"]], tensors[self.names["down"]]
+        self.dtype = dtype
+
+    def forward(self, x, step):
+        ops = step.ops
+        return ops.linear(ops.linear_activation(x, self.w_up, self.activation), self.w_down)
+
+
 register_part("feed_forward", "swiglu", SwiGlu)
+register_part("feed_forward", "dense", DenseMlp)

@@ -1,13 +1,13 @@
 """RMSNorm, fused with the residual addition that precedes it.
 
-`out = x * rsqrt(mean(x^2) + eps) * gamma`, all in 32-bit (src/transformer/norm.zig:6-33; device
+`out = x * rsqrt(mean(x^2) + eps) * gamma` (eps inside the root), all in 32-bit (src/transformer/norm.zig:6-33; device
 version src/cuda/layer_kernels.cu:17-43).  The reference adds residuals with separate kernels
 (`addKernel`, layer_kernels.cu:46-59); here the pending term is added into the 32-bit residual
 stream by the same kernel that normalises it.
 """
 from __future__ import annotations
 
-from .base import LazyNorm, Norm, ParamDecl, Residual, register_part
+from .base import LazyNorm, Norm, NormedTerm, ParamDecl, Residual, register_part
 
 
 class RmsNorm(Norm):
@@ -26,6 +26,13 @@ class RmsNorm(Norm):
 
     def forward(self, h, delta, step, lazy=False, rows=None):
         res = h if isinstance(h, Residual) else Residual(h)
+        if isinstance(delta, NormedTerm):
+            # the pending term is normed on its way into the stream, in the same kernel
+            ops = step.ops
+            if rows is not None:
+                picked = ops.gather_add(res.data, delta.data, rows, delta.gamma, delta.eps)
+                return ops.add_rmsnorm(picked, None, self.weight, self.eps, self.dtype)
+            return ops.add_rmsnorm(res.data, delta.data, self.weight, self.eps, self.dtype, delta.gamma, delta.eps)
         x = LazyNorm(res, delta, self.weight, self.eps, self.dtype, rows)
         if lazy and getattr(step.ops, "fuses_norm", False):
             return x
