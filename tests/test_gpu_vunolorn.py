@@ -1,0 +1,141 @@
+"""The Vunolorn hybrid on the GPU, whole models against the plain implementation (tests/plain_vunolorn.py):
+requests replayed through bin/trace_run whole, with the last tokens decoded one by one, in portions of changing
+size and mixed with other requests in a pool so small that pages and slots are used again, in 32-bit and in
+bfloat16; one far key that decides a row, at page borders, in prompts and in decoding; long decoding through the
+step graphs; greedy generation through the entry point."""
+import random
+
+import numpy as np
+import pytest
+import torch
+
+import plain_vunolorn as P
+import traces
+from test_vunolorn_cpu import echo_model, tokens
+from vunolorn_configs import ALL, ONLY, PAGE_SIZE
+from zig_ai_b200.config import config_from_dict
+from zig_ai_b200.weights import write_random_model
+
+pytestmark = pytest.mark.gpu
+
+LENGTHS = {"A": [70, 45, 128, 33, 7, 1, 2, 96], "B": [130, 61, 257, 40, 5, 1, 33, 90], "C": [300, 129, 64, 410, 1, 35]}
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    root = tmp_path_factory.mktemp("vunolorn_gpu")
+    out = {}
+    for name, (cfg, seed) in list(ALL.items()) + [("echo", (ONLY["echo"], 5))]:
+        d = str(root / name)
+        write_random_model(config_from_dict(cfg), seed, d, matrix_std="fan_in")
+        out[name] = d
+    return out
+
+
+@pytest.fixture(scope="module")
+def plain(models):
+    out = {}
+    for name in ALL:
+        c, W = P.read_config(models[name]), P.read_weights(models[name])
+        reqs = traces.requests_for(c["vocab"], LENGTHS[name], 77)
+        out[name] = (reqs, {k: P.forward(c, W, t).numpy() for k, t in reqs.items()})
+    return out
+
+
+def rows_of(got, tag, k, n):
+    return np.stack([got[(tag + k, p)] for p in range(n)])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_schedules_agree_with_plain(models, plain, tmp_path, name, dtype):
+    reqs, want = plain[name]
+    vocab = ALL[name][0]["vocab"]
+    steps = traces.number(traces.whole(reqs) + traces.decode_tail(reqs) + traces.portions(reqs, 3))
+    got = traces.run_trace(models[name], dtype, steps, max_tokens=512, out_dir=str(tmp_path / "o"), vocab=vocab,
+                           page_size=PAGE_SIZE[name])
+    for tag in "wdp":
+        for k, toks in reqs.items():
+            traces.check_request(rows_of(got, tag, k, len(toks)), want[k], dtype, f"{dtype} schedule '{tag}' request {k}")
+    for other in "dp":
+        for k, toks in reqs.items():
+            traces.check_same(rows_of(got, "w", k, len(toks)), rows_of(got, other, k, len(toks)), dtype,
+                              f"{dtype} schedules 'w'/'{other}' request {k}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_mixed_batches_in_a_small_pool(models, plain, tmp_path, name, dtype):
+    reqs, want = plain[name]
+    vocab = ALL[name][0]["vocab"]
+    longest = -(-max(len(t) for t in reqs.values()) // 64) * 64
+    max_tokens = longest + 128
+    steps = traces.number(traces.mixed(reqs, 5, max_tokens))
+    assert max(len(s["entries"]) for s in steps) >= 2
+    stats = {}
+    got = traces.run_trace(models[name], dtype, steps, max_tokens=max_tokens, out_dir=str(tmp_path / "o"), vocab=vocab,
+                           page_size=PAGE_SIZE[name], stats=stats)
+    for k, toks in reqs.items():
+        traces.check_request(rows_of(got, "m", k, len(toks)), want[k], dtype, f"{dtype} mixed, request {k}")
+    assert stats["pages_reused"] > 0 and stats["slots_used"] == 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("far_at", [0, 7, 8, 24])
+def test_one_far_key_decides(models, tmp_path, dtype, far_at):
+    from zig_ai_b200.engine.runner import load_runner
+    ps = 8
+    d = echo_model(models["echo"], str(tmp_path / "echo"))
+    V = P.read_config(d)["vocab"]
+    n = 9 * ps + 5
+    toks = tokens(V - 2, n, 50)
+    toks[far_at], toks[-1] = V - 2, V - 1
+    want = P.forward(P.read_config(d), P.read_weights(d), toks).numpy()
+    other = list(toks)
+    other[far_at] = 0
+    assert np.abs(P.forward(P.read_config(d), P.read_weights(d), other).numpy()[-1] - want[-1]).max() > 0.3
+    r = load_runner(d, dtype, max_tokens=128, max_requests=4, page_size=ps)
+    cuts = ([far_at] if far_at else []) + [1, ps - 1, 2 * ps + 1]
+    for rid, cut in (("w", [n]), ("d", [n - 3, 1, 1, 1]), ("p", cuts + [n - sum(cuts) - 2, 2])):
+        r.add_request(rid)
+        got, at = [], 0
+        for m in cut:
+            got.append(r.step([(rid, toks[at:at + m], list(range(m)))]).float().cpu().clone())
+            at += m
+        r.end_request(rid)
+        traces.check_request(torch.cat(got).numpy(), want, dtype, f"{dtype} far key at {far_at}, cut {rid}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_through_the_graphs(models, dtype):
+    from zig_ai_b200.engine.runner import load_runner
+    name = "C"
+    c, W = P.read_config(models[name]), P.read_weights(models[name])
+    toks = tokens(c["vocab"], 330, 60)
+    want = P.forward(c, W, toks).numpy()
+    r = load_runner(models[name], dtype, max_tokens=512, max_requests=4, page_size=64)
+    r.add_request("l")
+    got = [r.step([("l", toks[:30], list(range(30)))]).float().cpu().clone()]
+    for t in toks[30:]:
+        got.append(r.step([("l", [t], [0])]).float().cpu().clone())
+    assert r.graphs is not None and r.graphs.replays >= 290
+    traces.check_request(torch.cat(got).numpy(), want, dtype, f"{dtype} 300 decoded tokens")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["B", "C"])
+def test_greedy_generation_through_the_entry_point(models, name, dtype):
+    import zig_ai_b200 as z
+    g = random.Random(3)
+    c, W = P.read_config(models[name]), P.read_weights(models[name])
+    prompts = [[g.randrange(c["vocab"]) for _ in range(n)] for n in (9, 21, 2, 40, 1)]
+    eng = z.Engine(models[name], dtype, max_num_seqs=4, max_batched_tokens=16, max_model_len=128, page_size=PAGE_SIZE[name])
+    outs = eng.generate(prompts, max_new_tokens=12, temperature=0.0)
+    for p, out in zip(prompts, outs):
+        assert len(out) == 12
+        logits = P.forward(c, W, p + out)
+        for i, tok in enumerate(out):
+            row = logits[len(p) + i - 1]
+            slack = 1e-3 if dtype == "float32" else 8e-2 * float(row.abs().max())
+            assert float(row.max() - row[tok]) <= slack, f"{dtype}: token {i} of a request is not the plain implementation's choice"
+    assert eng.stats()["slots_used"] == 0

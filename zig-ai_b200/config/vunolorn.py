@@ -63,6 +63,19 @@ class VunolornConfig(ModelConfig):
     layers: List[Dict[str, Any]] = field(default_factory=list)
     max_positions: int = MAX_POSITIONS
 
+    # the names the engine and the command line use for every architecture
+    @property
+    def vocab_size(self) -> int:
+        return self.vocab
+
+    @property
+    def hidden_size(self) -> int:
+        return self.width
+
+    @property
+    def max_position_embeddings(self) -> int:
+        return self.max_positions
+
     @classmethod
     def from_dict(cls, d: Dict[str, Any]) -> "VunolornConfig":
         vocab, width = read_key(d, "vocab", int), read_key(d, "width", int)
@@ -118,4 +131,5 @@ class VunolornConfig(ModelConfig):
     def to_dict(self) -> Dict[str, Any]:
         return {"architecture": ARCHITECTURE, "vocab": self.vocab, "width": self.width,
                 "embedding": {"scale": self.embedding_scale}, "norm": {"eps": self.norm_eps},
-                "layers": copy.deepcopy(self.layers)}
+                "layers": copy.deepcopy(self.layers),
+                **({"max_positions": self.max_positions} if self.max_positions != MAX_POSITIONS else {})}
