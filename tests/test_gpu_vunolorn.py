@@ -18,6 +18,12 @@ from zig_ai_b200.weights import write_random_model
 
 pytestmark = pytest.mark.gpu
 
+# bfloat16 noise of this design on the small models, measured: rows up to 12 % of the request's logit scale (3 % on
+# average) where LFM2's tiny models show 5-6 % (2 %): every layer rounds the input of a recurrence that then
+# carries the error along, and the narrow widths (48, 64) average over few terms.  A lost state or key moves a
+# row by tens of per cent in the 32-bit run of the same schedule, which is held to 5e-5.
+BF16 = dict(bf16_row=0.25, bf16_mean=0.06)
+BF16_SAME = dict(bf16_row=0.4, bf16_mean=0.1)
 LENGTHS = {"A": [70, 45, 128, 33, 7, 1, 2, 96], "B": [130, 61, 257, 40, 5, 1, 33, 90], "C": [300, 129, 64, 410, 1, 35]}
 
 
@@ -56,11 +62,11 @@ def test_schedules_agree_with_plain(models, plain, tmp_path, name, dtype):
                            page_size=PAGE_SIZE[name])
     for tag in "wdp":
         for k, toks in reqs.items():
-            traces.check_request(rows_of(got, tag, k, len(toks)), want[k], dtype, f"{dtype} schedule '{tag}' request {k}")
+            traces.check_request(rows_of(got, tag, k, len(toks)), want[k], dtype, f"{dtype} schedule '{tag}' request {k}", **BF16)
     for other in "dp":
         for k, toks in reqs.items():
             traces.check_same(rows_of(got, "w", k, len(toks)), rows_of(got, other, k, len(toks)), dtype,
-                              f"{dtype} schedules 'w'/'{other}' request {k}")
+                              f"{dtype} schedules 'w'/'{other}' request {k}", **BF16_SAME)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -76,7 +82,7 @@ def test_mixed_batches_in_a_small_pool(models, plain, tmp_path, name, dtype):
     got = traces.run_trace(models[name], dtype, steps, max_tokens=max_tokens, out_dir=str(tmp_path / "o"), vocab=vocab,
                            page_size=PAGE_SIZE[name], stats=stats)
     for k, toks in reqs.items():
-        traces.check_request(rows_of(got, "m", k, len(toks)), want[k], dtype, f"{dtype} mixed, request {k}")
+        traces.check_request(rows_of(got, "m", k, len(toks)), want[k], dtype, f"{dtype} mixed, request {k}", **BF16)
     assert stats["pages_reused"] > 0 and stats["slots_used"] == 0
 
 
@@ -103,7 +109,7 @@ def test_one_far_key_decides(models, tmp_path, dtype, far_at):
             got.append(r.step([(rid, toks[at:at + m], list(range(m)))]).float().cpu().clone())
             at += m
         r.end_request(rid)
-        traces.check_request(torch.cat(got).numpy(), want, dtype, f"{dtype} far key at {far_at}, cut {rid}")
+        traces.check_request(torch.cat(got).numpy(), want, dtype, f"{dtype} far key at {far_at}, cut {rid}", **BF16)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -119,7 +125,7 @@ def test_long_decoding_through_the_graphs(models, dtype):
     for t in toks[30:]:
         got.append(r.step([("l", [t], [0])]).float().cpu().clone())
     assert r.graphs is not None and r.graphs.replays >= 290
-    traces.check_request(torch.cat(got).numpy(), want, dtype, f"{dtype} 300 decoded tokens")
+    traces.check_request(torch.cat(got).numpy(), want, dtype, f"{dtype} 300 decoded tokens", **BF16)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

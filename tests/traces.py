@@ -156,8 +156,9 @@ def request_errors(got_rows, want_rows):
     return np.sqrt(((got - want) ** 2).mean(axis=1)) / scale
 
 
-def check_request(got_rows, want_rows, dtype, where):
-    """All rows of one request against the plain implementation."""
+def check_request(got_rows, want_rows, dtype, where, bf16_row=1e-1, bf16_mean=3e-2):
+    """All rows of one request against the plain implementation.  (`bf16_row`, `bf16_mean`: the bfloat16 limits,
+    for a design whose measured 16-bit noise is another.)"""
     want = np.asarray(want_rows, dtype=np.float64)
     got = np.asarray(got_rows, dtype=np.float64)
     if dtype == "float32":
@@ -165,11 +166,11 @@ def check_request(got_rows, want_rows, dtype, where):
         assert err.max() < 5e-5, f"{where}: position {int(err.argmax())} is off by {err.max():.3e} of its largest logit"
     else:
         e = request_errors(got, want)
-        assert e.max() < 1e-1, f"{where}: position {int(e.argmax())} is off by {e.max():.3e} of the request's logit scale"
-        assert e.mean() < 3e-2, f"{where}: rows are off by {e.mean():.3e} of the request's logit scale on average"
+        assert e.max() < bf16_row, f"{where}: position {int(e.argmax())} is off by {e.max():.3e} of the request's logit scale"
+        assert e.mean() < bf16_mean, f"{where}: rows are off by {e.mean():.3e} of the request's logit scale on average"
 
 
-def check_same(a_rows, b_rows, dtype, where):
+def check_same(a_rows, b_rows, dtype, where, bf16_row=2e-1, bf16_mean=6e-2):
     """Two ways of running the same request.  In 32-bit they agree to the rounding of the sums.  In
     bfloat16 the two runs may go through different kernels (library product or few-rows kernel,
     span or single-token attention) and are two independent roundings; their distance is held to
@@ -180,4 +181,4 @@ def check_same(a_rows, b_rows, dtype, where):
         assert err.max() < 2e-5, f"{where}: position {int(err.argmax())} differs by {err.max():.3e}"
     else:
         e = request_errors(a, b)
-        assert e.max() < 2e-1 and e.mean() < 6e-2, f"{where}: two ways of cutting differ by {e.max():.3e} (mean {e.mean():.3e})"
+        assert e.max() < bf16_row and e.mean() < bf16_mean, f"{where}: two ways of cutting differ by {e.max():.3e} (mean {e.mean():.3e})"
