@@ -244,6 +244,8 @@ def run_ours(args):
     nums = model_numbers(cfg)
     if args.workload == "mixed":
         return run_mixed(args, cfg)
+    if args.only == "vunolorn":
+        return run_vunolorn(args)
     if args.only == "long":
         return run_long(args)
     if args.only == "sample":
@@ -338,6 +340,182 @@ def measure_shape(model, steps, warmup, page_size=64):
                          "frac_of_peak": round(step_bytes / (dev_ms * 1e-3) / 1e9 / hbm_peak, 3),
                          "launches_per_step": round(launches)})
     return rows, peak_src
+
+
+# ----------------------------------------------------------------------------- the Vunolorn hybrid beside LFM2
+def vunolorn_config(width, layers=16, vocab=65536):
+    """A Vunolorn model of a real model's proportions: groups of four layers (attention beside the minimal gated
+    recurrence with a dense feed-forward four times the width, two selective scans twice the width with 16 states,
+    a gated delta rule with value heads of 128), head size 64 throughout."""
+    heads = width // 64
+    group = [
+        {"type": "parallel", "mlp": {"kind": "dense", "ff": 4 * width},
+         "mixer": {"left": {"heads": heads, "kv_heads": heads // 2, "dim": 64, "vdim": 64, "scale": 0.125,
+                            "rot": {"base": 1000000.0, "dims": 64}},
+                   "right": {"width": width}, "left_scale": 1.0, "right_scale": 1.0}},
+        {"type": "mamba1", "mlp": None, "mixer": {"inner": 2 * width, "state": 16, "dt_rank": width // 16, "conv": 4}},
+        {"type": "mamba1", "mlp": None, "mixer": {"inner": 2 * width, "state": 16, "dt_rank": width // 16, "conv": 4}},
+        {"type": "delta", "mlp": None, "mixer": {"heads": heads, "kv_heads": heads // 2, "dim": 64, "vdim": 128, "conv": 4}},
+    ]
+    return {"architecture": "Vunolorn", "vocab": vocab, "width": width, "embedding": {"scale": float(width) ** 0.5},
+            "norm": {"eps": 1e-6}, "layers": [dict(group[i % 4]) for i in range(layers)]}
+
+
+def engine_numbers(eng):
+    """From the engine itself, for any architecture: matrix parameters a step reads, bytes of keys and values per
+    cached position, bytes of per-request state."""
+    decls = eng.runner.model.param_decls()
+    numel = lambda shape: int(__import__("math").prod(shape))
+    matrix = sum(numel(d.shape) for d in decls.values() if d.role == "matrix")
+    if getattr(eng.runner.model.head, "tied", False):
+        matrix += sum(numel(d.shape) for d in decls.values() if d.role == "table")
+    cache = eng.runner.cache
+    state = sum(len(g.members) * numel(g.need.shape) * 4 for g in cache.groups if not g.paged)
+    return dict(matrix_params=matrix, kv_bytes_per_token=cache.bytes_per_token(), state_bytes=state)
+
+
+def kernel_classes(eng, entries):
+    """Milliseconds per kernel class of one step launched kernel by kernel (CUDA events around every kernel
+    function; the shares are what it is for)."""
+    from zig_ai_b200.kernels import ops
+    runner = eng.runner
+    graphs, runner.use_graphs = runner.use_graphs, False
+    try:
+        for rid, _, _ in entries:
+            if not runner.has_request(rid):
+                runner.add_request(rid)
+        runner.step([(rid, toks, want) for rid, toks, want in entries])          # warm-up: same shapes
+        for rid, _, _ in entries:
+            runner.end_request(rid)
+            runner.add_request(rid)
+        ops.profile_begin()
+        runner.step([(rid, toks, want) for rid, toks, want in entries])
+        out = ops.profile_end()
+        for rid, _, _ in entries:
+            runner.end_request(rid)
+    finally:
+        runner.use_graphs = graphs
+    return {k: round(v, 4) for k, v in sorted(out.items(), key=lambda kv: -kv[1])}
+
+
+def recurrent_kernel_rooflines(width, hbm_peak):
+    """Each kernel of the recurrent mixers alone at the sizes of `vunolorn_config(width)`, beside LFM2's short
+    convolution at the same width (the like kernel of the closest model): a prompt portion of 2048 tokens of one
+    request and a step of 64 single tokens, timed with CUDA events over inputs that are rotated through more
+    memory than the L2 holds; bytes are what the kernel has to read and write once."""
+    import torch
+    from zig_ai_b200.engine.batch import pack_step
+    from zig_ai_b200.kernels import ops
+    dev, bf = torch.device("cuda"), torch.bfloat16
+    heads, G, D, V, I, S, R, W, L = width // 64, width // 128, 64, 128, 2 * width, 16, width // 16, width, 4
+    rows = []
+
+    def timed(f, n_sets):
+        for i in range(3):
+            f(i % n_sets)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        reps = 20
+        a.record()
+        for i in range(reps):
+            f(i % n_sets)
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / reps
+
+    for point, q_lens in (("prompt portion of 2048", [2048]), ("64 single tokens", [1] * 64)):
+        N, B = sum(q_lens), len(q_lens)
+        step = pack_step(ops, bf, dev, [(s, 100, [0] * n, [], s + 1) for s, n in enumerate(q_lens)],
+                         {0: [[1, 2] + [0] * 40 for _ in q_lens]})
+        n_sets = max(2, int(160e6 // max(N * 6 * I, 1)) + 1) if N > 64 else 24       # inputs and states rotate: more than L2
+        rnd = lambda *shape: [torch.randn(*shape, device=dev).to(bf) for _ in range(n_sets)]
+        st = lambda *shape: [torch.zeros(B + 1, *shape, device=dev) for _ in range(n_sets)]
+        # selective scan
+        x, proj, xz = rnd(N, I), rnd(N, R + 2 * S), rnd(N, 2 * I)
+        w_dt, b_dt, a_log, dsk = torch.randn(I, R, device=dev).to(bf) * 0.1, torch.zeros(I, device=dev), torch.zeros(I, S, device=dev), torch.ones(I, device=dev)
+        state = st(I, S)
+        ms = timed(lambda i: ops.selective_scan(x[i], proj[i], xz[i][:, I:], w_dt, b_dt, a_log, dsk, state[i], step, R), n_sets)
+        rows.append(("selective scan", point, ms, N * (3 * I + R + 2 * S) * 2 + B * I * S * 8))
+        # causal convolution (the scan's, 2W channels)
+        conv_w, conv_b, cstate = torch.randn(I, L, device=dev) * 0.1, torch.zeros(I, device=dev), st(L - 1, I)
+        ms = timed(lambda i: ops.causal_conv(xz[i][:, :I], conv_w, conv_b, cstate[i], step, True), n_sets)
+        rows.append(("causal convolution + SiLU", point, ms, N * 2 * I * 2 + B * (L - 1) * I * 8))
+        # minimal gated recurrence
+        zxg, gstate = rnd(N, 3 * W), st(W)
+        bz = torch.zeros(W, device=dev)
+        ms = timed(lambda i: ops.min_gru(zxg[i], bz, bz, gstate[i], step), n_sets)
+        rows.append(("minimal gated recurrence", point, ms, N * 4 * W * 2 + B * W * 8))
+        # gated delta rule (prepare + recurrence + output norm)
+        cols = 2 * G * D + heads * V
+        qkv, rest, dstate = rnd(N, cols), rnd(N, heads * V + 2 * heads), st(heads, D, V)
+        al, nw = torch.zeros(heads, device=dev), torch.ones(V, device=dev)
+        ms = timed(lambda i: ops.gated_delta(qkv[i], rest[i][:, heads * V:heads * V + heads], rest[i][:, heads * V + heads:],
+                                             rest[i][:, :heads * V], al, al, nw, 1e-6, dstate[i], step, heads, G, D, V), n_sets)
+        rows.append(("gated delta rule (3 kernels)", point, ms,
+                     N * (cols + 2 * heads * V + 2 * heads) * 2 + N * (2 * G * D + heads * V + 2 * heads) * 8 + B * heads * D * V * 8))
+        # LFM2's short convolution at the same width (3 taps, gates B and C): the like kernel of the closest model
+        bcx, sstate = rnd(N, 3 * W), st(2, W)
+        sw = torch.randn(W, 3, device=dev) * 0.1
+        ms = timed(lambda i: ops.short_conv(bcx[i], sw, None, sstate[i], step, 3), n_sets)
+        rows.append(("LFM2 short convolution", point, ms, N * 4 * W * 2 + B * 2 * W * 8))
+    return [{"kernel": k, "point": p, "width": width, "us": round(ms * 1e3, 2), "MB": round(b / 1e6, 3),
+             "GB_per_s": round(b / ms / 1e6, 1), "frac_of_copy_peak": round(b / ms / 1e6 / hbm_peak, 4)} for k, p, ms, b in rows]
+
+
+def run_vunolorn(args):
+    """Prefill and decode throughput of the Vunolorn hybrid at two widths beside the LFM2 shape of the same width,
+    layer count and vocabulary; the time of a prefill and of a decode step by kernel class; and the recurrent
+    kernels alone against the copy bandwidth.  JSON lines, then markdown tables."""
+    import torch
+    import zig_ai_b200 as z
+    from zig_ai_b200.config import config_from_dict
+    hbm_peak, flops_peak, peak_src = peaks()
+    rows, classes, kernels = [], [], []
+    for width, lfm2 in ((1024, "350m"), (2048, "1.2b")):
+        for label, cfg_dict in ((f"Vunolorn-{width}", vunolorn_config(width)), (f"LFM2-{lfm2.upper()}", shape_config(lfm2))):
+            cfg = config_from_dict(cfg_dict)
+            with tempfile.TemporaryDirectory(prefix="bench_hybrid_") as d:
+                z.write_random_model(cfg, 0, d)
+                eng = z.Engine(d, "bfloat16", max_num_seqs=64, max_batched_tokens=2048 + 64, max_model_len=CONTEXT,
+                               max_tokens=64 * CONTEXT, page_size=args.page_size)
+                nums = engine_numbers(eng)
+                prefill_ms = time_prefill(eng, reps=5)
+                T = PREFILL_TOKENS
+                rows.append({"model": label, "width": width, "matrix_params_M": round(nums["matrix_params"] / 1e6, 1),
+                             "point": "prefill 2048", "ms": round(prefill_ms, 3), "tokens_per_s": round(T / prefill_ms * 1e3),
+                             "matrix_TFLOP_per_s": round(2 * T * nums["matrix_params"] / prefill_ms / 1e9, 1)})
+                print(json.dumps(rows[-1]), flush=True)
+                for B in (1, 8, 64):
+                    dev_ms, e2e_ms, ctx_tokens, launches, _, _, _ = time_decode(eng, B, max(min(args.steps, 100), 20), args.warmup)
+                    step_bytes = 2 * nums["matrix_params"] + ctx_tokens * nums["kv_bytes_per_token"] + 2 * B * nums["state_bytes"]
+                    rows.append({"model": label, "width": width, "point": f"decode batch {B}", "ms": round(dev_ms, 4),
+                                 "e2e_ms": round(e2e_ms, 4), "tokens_per_s": round(B / dev_ms * 1e3),
+                                 "e2e_tokens_per_s": round(B / e2e_ms * 1e3), "GB_a_step": round(step_bytes / 1e9, 3),
+                                 "frac_of_copy_peak": round(step_bytes / (dev_ms * 1e-3) / 1e9 / hbm_peak, 3),
+                                 "launches_per_step": round(launches)})
+                    print(json.dumps(rows[-1]), flush=True)
+                g = random.Random(5)
+                V = eng.config.vocab_size
+                eng.flush()
+                pre = kernel_classes(eng, [("kc", [g.randrange(V) for _ in range(T)], [T - 1])])
+                dec = kernel_classes(eng, [(f"kc{i}", [g.randrange(V)], [0]) for i in range(64)])
+                classes.append({"model": label, "prefill_2048_ms_by_class": pre, "decode_64_first_token_ms_by_class": dec})
+                print(json.dumps(classes[-1]), flush=True)
+                del eng
+                torch.cuda.empty_cache()
+        kernels += recurrent_kernel_rooflines(width, hbm_peak)
+    for r in kernels:
+        print(json.dumps(r), flush=True)
+    print(f"\npeaks ({peak_src}): {hbm_peak:.0f} GB/s copy bandwidth, {flops_peak:.0f} TFLOP/s bf16 product (burst)\n")
+    print("| model | point | ms a step (device) | tokens/s (device) | tokens/s (end to end) | of the copy peak |")
+    print("|---|---|---|---|---|---|")
+    for r in rows:
+        print(f"| {r['model']} | {r['point']} | {r['ms']} | {r['tokens_per_s']} | {r.get('e2e_tokens_per_s', '')} | {r.get('frac_of_copy_peak', '')} |")
+    print("\n| kernel | point | width | us | MB | GB/s | of the copy peak |")
+    print("|---|---|---|---|---|---|---|")
+    for r in kernels:
+        print(f"| {r['kernel']} | {r['point']} | {r['width']} | {r['us']} | {r['MB']} | {r['GB_per_s']} | {r['frac_of_copy_peak']} |")
+    return 0
 
 
 def run_table(args):
@@ -693,9 +871,10 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "gemm", "timeline", "table", "stream", "long", "sample"],
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "gemm", "timeline", "table", "stream", "long", "sample", "vunolorn"],
                     help="profiling aid: run only the batch-8 decode steps or only the prefill (prints a short line); "
-                         "table: every figure of the 350M, 700M and 1.2B shapes (profiles/measurements.md)")
+                         "table: every figure of the 350M, 700M and 1.2B shapes (profiles/measurements.md); vunolorn: the "
+                         "Vunolorn hybrid at two widths beside LFM2 at equal width, and its recurrent kernels alone")
     ap.add_argument("--batch", type=int, default=8, help="with --only decode: the batch size; with --only stream: 24, 64 or "
                                                          "128 runs that row count only")
     ap.add_argument("--profile-range", action="store_true",
