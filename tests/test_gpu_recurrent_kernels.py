@@ -12,7 +12,9 @@ from test_gpu_kernels import make_step
 pytestmark = pytest.mark.gpu
 
 DTYPES = [torch.float32, torch.bfloat16]
-STEPS = ([1, 3, 4, 11, 1], [5, 1, 1, 2, 9], [1, 1, 1, 1, 1], [2, 37, 1, 1, 6])
+# the last two are long enough for the passes over chunks of rows (chunks that end inside and at a request's end,
+# a request shorter than a chunk, one of exactly two chunks)
+STEPS = ([1, 3, 4, 11, 1], [5, 1, 1, 2, 9], [1, 1, 1, 1, 1], [2, 37, 1, 1, 6], [200, 1, 63, 128, 70], [64, 65, 300, 2, 1])
 
 
 def ops():
@@ -36,7 +38,7 @@ def test_causal_conv_spans_and_state(dtype, C, L, bias, act):
     state_a = torch.randn(6, max(L - 1, 1), C, generator=g).cuda()
     state_b = state_a.clone()
     for q_lens in STEPS:
-        step = make_step(o, dtype, [3] * 5, q_lens, 8, 64, 5)
+        step = make_step(o, dtype, [3] * 5, q_lens, 8, 256, 5)
         wide = torch.randn(sum(q_lens), C + 24, generator=g).to(dtype).cuda()
         x = wide[:, 8:8 + C]                                   # a column slice of a wider matrix
         ya = o.causal_conv(x, w, b, state_a, step, act, True)
@@ -63,7 +65,7 @@ def test_selective_scan(dtype, I, S, R):
     state_a = torch.randn(6, I, S, generator=g).cuda()
     state_b = state_a.clone()
     for q_lens in STEPS:
-        step = make_step(o, dtype, [3] * 5, q_lens, 8, 64, 5)
+        step = make_step(o, dtype, [3] * 5, q_lens, 8, 256, 5)
         N = sum(q_lens)
         x = torch.randn(N, I, generator=g).to(dtype).cuda()
         proj = torch.randn(N, R + 2 * S + 3, generator=g).to(dtype).cuda()
@@ -84,7 +86,7 @@ def test_min_gru(dtype, W):
     state_a = torch.randn(6, W, generator=g).cuda()
     state_b = state_a.clone()
     for q_lens in STEPS:
-        step = make_step(o, dtype, [3] * 5, q_lens, 8, 64, 5)
+        step = make_step(o, dtype, [3] * 5, q_lens, 8, 256, 5)
         zxg = (torch.randn(sum(q_lens), 3 * W, generator=g) * 2).to(dtype).cuda()
         ya = o.min_gru(zxg, bz, bx, state_a, step, True)
         yb = ref_ops.min_gru(zxg, bz, bx, state_b, step, True)
@@ -105,7 +107,7 @@ def test_gated_delta(dtype, H, G, D, V):
     state_b = state_a.clone()
     cols = 2 * G * D + H * V
     for q_lens in STEPS:
-        step = make_step(o, dtype, [3] * 5, q_lens, 8, 64, 5)
+        step = make_step(o, dtype, [3] * 5, q_lens, 8, 256, 5)
         N = sum(q_lens)
         qkv = torch.randn(N, cols, generator=g).to(dtype).cuda()
         rest = torch.randn(N, H * V + 2 * H, generator=g).to(dtype).cuda()

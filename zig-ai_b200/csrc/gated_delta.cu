@@ -7,7 +7,8 @@
 //   * prepare: unit norms, beta and g for every row of the step, all 32-bit;
 //   * the recurrence: the columns of S are independent, so a block owns some columns of one head of one
 //     request and walks the request's rows in order; P lanes of a warp share a column, each with DP of
-//     its D rows in registers; the next token's operands are loaded while the current one is computed;
+//     its D rows in registers; the operands of the next sixteen tokens come into shared memory by
+//     asynchronous copies while the current sixteen are computed;
 //   * the output norm: o / rms(o) * weight * silu(gate) per head, rounded to the model's dtype.
 #include "common.cuh"
 
@@ -42,16 +43,33 @@ __global__ void delta_prepare_kernel(float* __restrict__ qk_out, float* __restri
     }
 }
 
+__device__ __forceinline__ void cp_async4(void* smem, const void* gmem) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((unsigned)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
+// The operands of TB tokens (a stage of the ring; fewer where a head is large, so that two stages fit) in shared memory: per token k and q of the head (each P groups of DP values,
+// a group padded to DP + 4 so that the P groups read by one warp lie in different banks, 16-byte aligned), beta, g,
+// and the block's columns of v as 32-bit values.
+template <int DP, int P>
+struct DeltaStage {
+    static constexpr int GROUP = DP + 4, KQ = P * GROUP, VB = 128 / P, PER_TOKEN = 2 * KQ + 4 + VB;
+    static constexpr int TB = DP * P > 128 ? 8 : 16;
+};
+
 template <typename T, int DP, int P>
 __global__ void __launch_bounds__(128) gated_delta_kernel(
     float* __restrict__ o_out, const float* __restrict__ qk, const float* __restrict__ bg, const T* __restrict__ v_in,
     int v_stride, float* __restrict__ state, const int* __restrict__ cu_q, const int* __restrict__ slot_ids, int H, int G,
     int D, int V, int write_state, int num_slots, int* __restrict__ status) {
+    using St = DeltaStage<DP, P>;
+    constexpr int VB = St::VB, TB = St::TB;
+    __shared__ __align__(16) float ring[2][TB][St::PER_TOKEN];
     pdl_trigger();
     pdl_wait();
-    constexpr int VB = 128 / P;
-    const int seq = blockIdx.x, h = blockIdx.y, p = threadIdx.x % P;
-    int j = blockIdx.z * VB + threadIdx.x / P;
+    const int seq = blockIdx.x, h = blockIdx.y, p = threadIdx.x % P, jl = threadIdx.x / P;
+    const int j0 = blockIdx.z * VB;
+    int j = j0 + jl;
     const bool live = j < V;
     if (!live) j = V - 1;                              // (stays for the shuffles, stores nothing)
     const int start = cu_q[seq], end = cu_q[seq + 1];
@@ -59,49 +77,86 @@ __global__ void __launch_bounds__(128) gated_delta_kernel(
     const int slot = zai_checked_slot(slot_ids[seq], num_slots, status);
     const int kvh = h / (H / G), d0 = p * DP;
     float* st = state + (((size_t)slot * H + h) * D) * V + j;
-    float S[DP], kc[DP], qc[DP], kn[DP], qn[DP];
+    float S[DP];
 #pragma unroll
     for (int i = 0; i < DP; ++i) S[i] = d0 + i < D ? st[(size_t)(d0 + i) * V] : 0.f;
-    auto load = [&](int t, float (&kk)[DP], float (&qq)[DP], float& beta, float& g, float& vv) {
-        const float* qrow = qk + ((size_t)t * 2 * G + kvh) * D + d0;
-        const float* krow = qk + ((size_t)t * 2 * G + G + kvh) * D + d0;
-#pragma unroll
-        for (int i = 0; i < DP; ++i) {
-            kk[i] = d0 + i < D ? krow[i] : 0.f;
-            qq[i] = d0 + i < D ? qrow[i] : 0.f;
+    for (int i = threadIdx.x; i < 2 * TB * St::PER_TOKEN; i += 128) (&ring[0][0][0])[i] = 0.f;   // rows of k, q beyond D stay zero
+    __syncthreads();
+
+    // a stage's k, q, beta, g by asynchronous copies; its v columns through registers (converted to 32-bit)
+    constexpr int V_PER_THREAD = (TB * VB + 127) / 128;
+    float v_regs[V_PER_THREAD];
+    auto issue = [&](int t0, int buf) {
+        const int n = min(TB, end - t0);
+        for (int r = threadIdx.x; r < 2 * D; r += 128) {                                  // an element of k | q, for every token
+            const int which = r >= D, d = which ? r - D : r;                              // which: 0 k, 1 q
+            const float* src = qk + ((size_t)t0 * 2 * G + (which ? 0 : G) + kvh) * D + d;
+            float* dst = &ring[buf][0][which * St::KQ + (d / DP) * St::GROUP + d % DP];
+            for (int tok = 0; tok < n; ++tok) cp_async4(dst + tok * St::PER_TOKEN, src + (size_t)tok * 2 * G * D);
         }
-        beta = bg[(size_t)t * 2 * H + h];
-        g = bg[(size_t)t * 2 * H + H + h];
-        vv = to_float(v_in[(size_t)t * v_stride + (size_t)h * V + j]);
+        for (int i = threadIdx.x; i < n * 2; i += 128) {
+            const int tok = i / 2, which = i % 2;                                        // 0 beta, 1 g
+            cp_async4(&ring[buf][tok][2 * St::KQ + which], bg + (size_t)(t0 + tok) * 2 * H + which * H + h);
+        }
+#pragma unroll
+        for (int e = 0; e < V_PER_THREAD; ++e) {
+            const int i = threadIdx.x + e * 128, tok = i / VB, col = i % VB;
+            v_regs[e] = (tok < n && j0 + col < V) ? to_float(v_in[(size_t)(t0 + tok) * v_stride + (size_t)h * V + j0 + col]) : 0.f;
+        }
     };
-    float beta, g, vv, beta_n = 0.f, g_n = 0.f, vv_n = 0.f;
-    load(start, kc, qc, beta, g, vv);
-    for (int t = start; t < end; ++t) {
-        if (t + 1 < end) load(t + 1, kn, qn, beta_n, g_n, vv_n);
-        float dot = 0.f;
+    auto land = [&](int buf) {
+        cp_async_wait_all();
 #pragma unroll
-        for (int i = 0; i < DP; ++i) {
-            S[i] *= g;
-            dot += S[i] * kc[i];
+        for (int e = 0; e < V_PER_THREAD; ++e) {
+            const int i = threadIdx.x + e * 128, tok = i / VB, col = i % VB;
+            if (tok < TB) ring[buf][tok][2 * St::KQ + 4 + col] = v_regs[e];
         }
+        __syncthreads();
+    };
+    issue(start, 0);
+    land(0);
+    int buf = 0;
+    for (int t0 = start; t0 < end; t0 += TB, buf ^= 1) {
+        const bool more = t0 + TB < end;
+        if (more) issue(t0 + TB, buf ^ 1);
+        const int n = min(TB, end - t0);
+        for (int tok = 0; tok < n; ++tok) {
+            const float* row = ring[buf][tok];
+            float kc[DP], qc[DP];
 #pragma unroll
-        for (int o = P / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-        const float u = beta * (vv - dot);
-        float out = 0.f;
+            for (int i = 0; i < DP; i += 4) {
+                const float4 a = *reinterpret_cast<const float4*>(row + p * St::GROUP + i);
+                const float4 b = *reinterpret_cast<const float4*>(row + St::KQ + p * St::GROUP + i);
+                kc[i] = a.x; kc[i + 1] = a.y; kc[i + 2] = a.z; kc[i + 3] = a.w;
+                qc[i] = b.x; qc[i + 1] = b.y; qc[i + 2] = b.z; qc[i + 3] = b.w;
+            }
+            const float beta = row[2 * St::KQ], g = row[2 * St::KQ + 1], vv = row[2 * St::KQ + 4 + jl];
+            float dot0 = 0.f, dot1 = 0.f;
 #pragma unroll
-        for (int i = 0; i < DP; ++i) {
-            S[i] += kc[i] * u;
-            out += S[i] * qc[i];
+            for (int i = 0; i < DP; i += 2) {
+                S[i] *= g;
+                S[i + 1] *= g;
+                dot0 += S[i] * kc[i];
+                dot1 += S[i + 1] * kc[i + 1];
+            }
+            float dot = dot0 + dot1;
+#pragma unroll
+            for (int o = P / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+            const float u = beta * (vv - dot);
+            float out0 = 0.f, out1 = 0.f;
+#pragma unroll
+            for (int i = 0; i < DP; i += 2) {
+                S[i] += kc[i] * u;
+                S[i + 1] += kc[i + 1] * u;
+                out0 += S[i] * qc[i];
+                out1 += S[i + 1] * qc[i + 1];
+            }
+            float out = out0 + out1;
+#pragma unroll
+            for (int o = P / 2; o > 0; o >>= 1) out += __shfl_xor_sync(0xffffffffu, out, o);
+            if (p == 0 && live) o_out[(size_t)(t0 + tok) * H * V + (size_t)h * V + j] = out;
         }
-#pragma unroll
-        for (int o = P / 2; o > 0; o >>= 1) out += __shfl_xor_sync(0xffffffffu, out, o);
-        if (p == 0 && live) o_out[(size_t)t * H * V + (size_t)h * V + j] = out;
-#pragma unroll
-        for (int i = 0; i < DP; ++i) {
-            kc[i] = kn[i];
-            qc[i] = qn[i];
-        }
-        beta = beta_n; g = g_n; vv = vv_n;
+        if (more) land(buf ^ 1);
     }
     if (write_state && live) {
 #pragma unroll

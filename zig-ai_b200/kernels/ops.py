@@ -37,8 +37,8 @@ _SIGNATURES = {
                    "zai_weighted_sum": [_P, _P, _P, _I, _F, _F, ctypes.c_longlong, _P]},
     "causal_conv": {"zai_causal_conv": [_P, _I, _P, _I, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P]},
     "selective_scan": {"zai_selective_scan": [_P, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I,
-                                              _I, _P, _P]},
-    "min_gru": {"zai_min_gru": [_P, _P, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P]},
+                                              _I, _P, _P, _P, _P, _I, _I, _I, _P]},
+    "min_gru": {"zai_min_gru": [_P, _P, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _I, _I, _P]},
     "gated_delta": {
         "zai_delta_prepare": [_P, _P, _P, _I, _P, _P, _I, _I, _P, _P, _I, _I, _I, _I, _F, _P],
         "zai_gated_delta": [_P, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
@@ -396,6 +396,8 @@ def _skinny(x, w, epilogue, out_cols, out_dtype):
     M = (x.rows.numel() if x.rows is not None else x.residual.data.shape[0]) if lazy else x.shape[0]
     O, K = w.shape
     if w.dtype != torch.bfloat16 or (not lazy and x.dtype != torch.bfloat16) or (lazy and x.dtype != torch.bfloat16):
+        return None
+    if not lazy and not x.is_contiguous():
         return None
     if not _fn("decode_gemm", "zai_skinny_gemm_supports")(M, O, K, epilogue, int(lazy)):
         return None
@@ -956,6 +958,19 @@ def weighted_sum(a, b, wa, wb):
     return out
 
 
+CHUNKED_SCAN_MIN_ROWS = 256     # steps with prompt portions of this many rows or more run the linear recurrences in chunks
+
+
+def _scan_chunks(step, n_rows):
+    """(rows per chunk, upper bound of the chunks) for a recurrence that is linear in its state, or (0, 0) where
+    the rows of each request are walked in one pass: steps of single tokens and small steps.  Both depend only on
+    the step's row and request counts, which a captured step shape keeps."""
+    if step.decode_only or n_rows < CHUNKED_SCAN_MIN_ROWS:
+        return 0, 0
+    chunk = 64 if n_rows <= 8192 else 256
+    return chunk, n_rows // chunk + step.n_seqs
+
+
 def _rows_view(x):
     """(pointer, row stride) of a 2-D tensor whose rows are contiguous (a column slice of a wider matrix)."""
     if x.dim() != 2 or x.stride(1) != 1 or not x.is_cuda:
@@ -997,10 +1012,17 @@ def selective_scan(x, proj, z, w_dt, b_dt, a_log, d_skip, state, step, dt_rank, 
     if state.dtype != torch.float32 or tuple(state.shape[1:]) != (I, S):
         raise KernelError("the scan state is 32-bit [slots, inner, state]")
     y = torch.empty((N, I), dtype=x.dtype, device=x.device)
+    chunk, max_chunks = _scan_chunks(step, N)
+    ends = torch.empty((max_chunks, I, S), dtype=torch.float32, device=x.device) if chunk else None
+    sums = torch.empty((max_chunks, I), dtype=torch.float32, device=x.device) if chunk else None
+    # long portions: the step sizes' products for all rows as one matrix product (32-bit result)
+    dt_raw = _library_product(proj[:, :R], w_dt, torch.float32) if chunk else None
     _check(_fn("selective_scan", "zai_selective_scan")(
         _ptr(y), _ptr(x), pp, ps, zp, zs, _dt(x), _ptr(w_dt), _ptr(b_dt), _ptr(a_log), _ptr(d_skip), _ptr(state),
         _ptr(step.cu_q), _ptr(step.slot_ids), N, step.n_seqs, I, S, R, int(bool(write_state)), state.shape[0],
-        _status_ptr(x.device), _stream()), "selective_scan")
+        _status_ptr(x.device), _ptr(ends), _ptr(sums), _ptr(dt_raw), chunk, max_chunks, int(bool(step.decode_only)), _stream()),
+        "selective_scan",
+        3 if chunk else 1)
     return y
 
 
@@ -1014,9 +1036,12 @@ def min_gru(zxg, b_z, b_x, state, step, write_state=True):
     if state.dtype != torch.float32 or tuple(state.shape[1:]) != (W,):
         raise KernelError("the recurrence's state is 32-bit [slots, width]")
     out = torch.empty((N, W), dtype=zxg.dtype, device=zxg.device)
+    chunk, max_chunks = _scan_chunks(step, N)
+    ends = torch.empty((2, max_chunks, W), dtype=torch.float32, device=zxg.device) if chunk else None
     _check(_fn("min_gru", "zai_min_gru")(_ptr(out), p, stride, _dt(zxg), _ptr(b_z), _ptr(b_x), _ptr(state), _ptr(step.cu_q),
                                          _ptr(step.slot_ids), N, step.n_seqs, W, int(bool(write_state)), state.shape[0],
-                                         _status_ptr(zxg.device), _stream()), "min_gru")
+                                         _status_ptr(zxg.device), _ptr(ends), _ptr(ends[1]) if chunk else None, chunk, max_chunks,
+                                         _stream()), "min_gru", 3 if chunk else 1)
     return out
 
 
