@@ -115,7 +115,8 @@ __global__ void __launch_bounds__(128) gated_delta_kernel(
     };
     issue(start, 0);
     land(0);
-    int buf = 0;
+    int buf = 0, pend_t = -1;
+    float pend_out = 0.f;
     for (int t0 = start; t0 < end; t0 += TB, buf ^= 1) {
         const bool more = t0 + TB < end;
         if (more) issue(t0 + TB, buf ^ 1);
@@ -131,32 +132,39 @@ __global__ void __launch_bounds__(128) gated_delta_kernel(
                 qc[i] = b.x; qc[i + 1] = b.y; qc[i + 2] = b.z; qc[i + 3] = b.w;
             }
             const float beta = row[2 * St::KQ], g = row[2 * St::KQ + 1], vv = row[2 * St::KQ + 4 + jl];
-            float dot0 = 0.f, dot1 = 0.f;
+            // a warp issues in order: four short chains of multiply-adds instead of one long one, and the last
+            // token's read-out is summed over the lanes beside this token's S^T k (two exchanges in flight at once)
+            float d4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int i = 0; i < DP; i += 2) {
+            for (int i = 0; i < DP; ++i) {
                 S[i] *= g;
-                S[i + 1] *= g;
-                dot0 += S[i] * kc[i];
-                dot1 += S[i + 1] * kc[i + 1];
+                d4[i & 3] += S[i] * kc[i];
             }
-            float dot = dot0 + dot1;
+            float dot = (d4[0] + d4[1]) + (d4[2] + d4[3]);
+            float po = pend_out;
 #pragma unroll
-            for (int o = P / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+            for (int o = P / 2; o > 0; o >>= 1) {
+                dot += __shfl_xor_sync(0xffffffffu, dot, o);
+                po += __shfl_xor_sync(0xffffffffu, po, o);
+            }
+            if (pend_t >= 0 && p == 0 && live) o_out[(size_t)pend_t * H * V + (size_t)h * V + j] = po;
             const float u = beta * (vv - dot);
-            float out0 = 0.f, out1 = 0.f;
+            float o4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int i = 0; i < DP; i += 2) {
+            for (int i = 0; i < DP; ++i) {
                 S[i] += kc[i] * u;
-                S[i + 1] += kc[i + 1] * u;
-                out0 += S[i] * qc[i];
-                out1 += S[i + 1] * qc[i + 1];
+                o4[i & 3] += S[i] * qc[i];
             }
-            float out = out0 + out1;
-#pragma unroll
-            for (int o = P / 2; o > 0; o >>= 1) out += __shfl_xor_sync(0xffffffffu, out, o);
-            if (p == 0 && live) o_out[(size_t)(t0 + tok) * H * V + (size_t)h * V + j] = out;
+            pend_out = (o4[0] + o4[1]) + (o4[2] + o4[3]);
+            pend_t = t0 + tok;
         }
         if (more) land(buf ^ 1);
+    }
+    {
+        float po = pend_out;                           // the last token's read-out
+#pragma unroll
+        for (int o = P / 2; o > 0; o >>= 1) po += __shfl_xor_sync(0xffffffffu, po, o);
+        if (pend_t >= 0 && p == 0 && live) o_out[(size_t)pend_t * H * V + (size_t)h * V + j] = po;
     }
     if (write_state && live) {
 #pragma unroll

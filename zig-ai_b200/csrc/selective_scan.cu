@@ -6,15 +6,15 @@
 //   y[t, c]   = ( sum_n h[c, n] * C[t, n] + D[c] * x[t, c] ) * silu(z[t, c])
 //
 // Everything but the stored activations (x, p, z, y in the model's dtype) is 32-bit: the step size, the
-// decay, the state and the sums.  G lanes of a warp share a channel, each with K consecutive ones of its S
-// states in registers.  Tokens are taken four or eight at a time: the loads, step sizes and decays of the group
-// do not depend on the state and are in flight together, only the state's own multiply-adds wait for one another.
+// decay, the state and the sums.  The products dt_in . Wdt^T of all rows are one matrix product made beforehand
+// (on the tensor cores where the model is bfloat16).  A lane holds K consecutive states of a channel in registers:
+// a whole channel where S <= 16, else G lanes of a warp share it.  Rows are taken two or four at a time: the loads,
+// step sizes and decays of the group do not depend on the state and are in flight together, only the state's own
+// multiply-adds wait for one another.
 //
 // Two ways through a step:
-//   * one pass (steps of single tokens and short portions): a block walks one request's rows in order; the
-//     R-term product for the step size is split over the channel's lanes;
-//   * three passes (long portions): the step sizes' products for all rows are one matrix product made beforehand
-//     (on the tensor cores), and the rows of every request are cut into chunks of `chunk` tokens.
+//   * one pass (steps of single tokens and short portions): a block walks one request's rows in order;
+//   * three passes (long portions): the rows of every request are cut into chunks of `chunk` tokens.
 //     Pass 1 walks every chunk from a zero state and keeps its end state E and its summed step sizes
 //     (the chunk's decay is exp(A * sum dt)); pass 2 carries the state across the chunks of a request,
 //     h_in(j+1) = exp(A sum_j) h_in(j) + E_j, starting from the stored state, and stores the request's new
@@ -31,14 +31,9 @@ template <> __device__ __forceinline__ float softplus_for<bf16>(float v) { retur
 template <typename T> __device__ __forceinline__ float silu_for(float v) { return v / (1.f + expf(-v)); }
 template <> __device__ __forceinline__ float silu_for<bf16>(float v) { return __fdividef(v, 1.f + __expf(-v)); }
 
-#ifndef ZAI_SCAN_PRE_U
-#define ZAI_SCAN_PRE_U 4        // rows in flight per lane in the passes over chunks
-#endif
-#define ZAI_SCAN_WREGS 32       // step-size weights a lane keeps in registers (R <= G * this), else they are re-read
-
 // The chunk with index b among all chunks of the step (requests in order, each cut into chunks of Lc rows).
 __device__ __forceinline__ bool zai_find_chunk(const int* __restrict__ cu_q, int n_seqs, int Lc, int b, int& seq, int& t0,
-                                               int& t1, int& last) {
+                                               int& t1) {
     for (int s = 0; s < n_seqs; ++s) {
         const int a = cu_q[s], e = cu_q[s + 1];
         const int nc = (e - a + Lc - 1) / Lc;
@@ -46,7 +41,6 @@ __device__ __forceinline__ bool zai_find_chunk(const int* __restrict__ cu_q, int
             seq = s;
             t0 = a + b * Lc;
             t1 = min(t0 + Lc, e);
-            last = b == nc - 1;
             return true;
         }
         b -= nc;
@@ -76,73 +70,50 @@ __device__ __forceinline__ void load_run(const bf16* p, float (&d)[K], int n_val
     }
 }
 
-// Walks rows [t0, t1) of one request for channel c; this lane holds the states g*K .. g*K + K - 1.  EMIT: writes y.
-// PRE: the step sizes' products come from `dt_raw` [N, I] (32-bit, a matrix product made beforehand) instead of
-// being summed here.  U tokens are in flight together.  sum_dt (if not null) receives the sum of the step sizes.
 __device__ __forceinline__ void prefetch_l1(const void* p) { asm volatile("prefetch.global.L1 [%0];" ::"l"(p)); }
 
-template <typename T, int K, int G, bool EMIT, bool PRE, int U>
+// Walks rows [t0, t1) of one request for channel c; this lane holds the states g*K .. g*K + K - 1 (with 16 states
+// or fewer one lane holds a channel's whole state: nothing is exchanged between lanes, and the rows' B and C are
+// the same addresses for every lane of a warp).  `dt_raw` [N, I] holds the step sizes' products dt_in . Wdt^T in
+// 32-bit (a matrix product made beforehand).  EMIT: writes y.  U rows are in flight together.  PREFETCH: the rows
+// are first asked into L1 (one trip to memory for a chunk, not one per group of rows).
+template <typename T, int K, int G, bool EMIT, int U, bool PREFETCH>
 __device__ __forceinline__ void scan_walk(float (&h)[K], const float (&a)[K], int t0, int t1, int c, int g, bool live,
                                           T* __restrict__ y, const T* __restrict__ x, const T* __restrict__ proj, int proj_stride,
-                                          const T* __restrict__ z, int z_stride, const T* __restrict__ wrow,
-                                          const float* __restrict__ dt_raw, float bias, float dsk, int I, int S, int R,
-                                          float* sum_dt) {
-    if (PRE) {
-        // a chunk's rows are asked into L1 at once (one trip to memory for the chunk, not one per group of rows):
-        // per row the block's 128 / G channels of x, z and dt_raw, and the row of B and C
+                                          const T* __restrict__ z, int z_stride, const float* __restrict__ dt_raw, float bias,
+                                          float dsk, int I, int S, int R, float* sum_dt) {
+    if (PREFETCH) {
         const int c0 = blockIdx.y * (128 / G);
         for (int tt = t0 + threadIdx.x; tt < t1; tt += 128) {
-            prefetch_l1(x + (size_t)tt * I + c0);
-            if (EMIT) prefetch_l1(z + (size_t)tt * z_stride + c0);
-            prefetch_l1(dt_raw + (size_t)tt * I + c0);
             const T* p = proj + (size_t)tt * proj_stride + R;
             for (int o = 0; o < (int)(2 * S * sizeof(T)); o += 128) prefetch_l1(reinterpret_cast<const char*>(p) + o);
+            for (int o = 0; o < 128 / G; o += 32) {
+                prefetch_l1(dt_raw + (size_t)tt * I + c0 + o);
+                if (o % 64 == 0) {
+                    prefetch_l1(x + (size_t)tt * I + c0 + o);
+                    if (EMIT) prefetch_l1(z + (size_t)tt * z_stride + c0 + o);
+                }
+            }
         }
-    }
-    float w[PRE ? 1 : ZAI_SCAN_WREGS];
-    const bool w_in_regs = !PRE && R <= G * ZAI_SCAN_WREGS && t1 - t0 > 2;
-    if (w_in_regs) {
-#pragma unroll
-        for (int i = 0; i < (PRE ? 1 : ZAI_SCAN_WREGS); ++i) w[i] = g + i * G < R ? to_float(wrow[g + i * G]) : 0.f;
     }
     const int n_mine = max(min(S - g * K, K), 0);
     const bool vec = sizeof(T) == 2 && ((proj_stride | R | S) & 3) == 0 && (reinterpret_cast<uintptr_t>(proj) & 7) == 0;
     float total = 0.f;
     for (int t = t0; t < t1; t += U) {
-        float acc[U], xv[U], zv[U], bv[U][K], cv[U][K];
+        float dt[U], xv[U], zv[U], bv[U][K], cv[U][K];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             const bool on = t + u < t1;
             const int tt = on ? t + u : t;
-            const T* p = proj + (size_t)tt * proj_stride;
-            float s = 0.f;
-            if (PRE) {
-                if (on) s = dt_raw[(size_t)tt * I + c];
-            } else if (on) {
-                if (w_in_regs) {
-#pragma unroll
-                    for (int i = 0; i < (PRE ? 1 : ZAI_SCAN_WREGS); ++i)
-                        if (g + i * G < R) s += w[i] * to_float(p[g + i * G]);
-                } else {
-                    for (int r = g; r < R; r += G) s += to_float(wrow[r]) * to_float(p[r]);
-                }
-            }
-            acc[u] = s;
+            const T* p = proj + (size_t)tt * proj_stride + R + g * K;
+            dt[u] = on ? dt_raw[(size_t)tt * I + c] : 0.f;
             xv[u] = on ? to_float(x[(size_t)tt * I + c]) : 0.f;
             zv[u] = (EMIT && on) ? to_float(z[(size_t)tt * z_stride + c]) : 0.f;
-            load_run<K>(p + R + g * K, bv[u], on ? n_mine : 0, vec);
-            if (EMIT) load_run<K>(p + R + S + g * K, cv[u], on ? n_mine : 0, vec);
+            load_run<K>(p, bv[u], on ? n_mine : 0, vec);
+            if (EMIT) load_run<K>(p + S, cv[u], on ? n_mine : 0, vec);
         }
-        float dt[U];
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-            float s = acc[u];
-            if (!PRE) {
-#pragma unroll
-                for (int o = G / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-            }
-            dt[u] = softplus_for<T>(s + bias);
-        }
+        for (int u = 0; u < U; ++u) dt[u] = softplus_for<T>(dt[u] + bias);
         float out[U];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
@@ -163,19 +134,37 @@ __device__ __forceinline__ void scan_walk(float (&h)[K], const float (&a)[K], in
                 float s = out[u];
 #pragma unroll
                 for (int o = G / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-                if (g == 0 && live && t + u < t1)
-                    y[(size_t)(t + u) * I + c] = from_float<T>((s + dsk * xv[u]) * silu_for<T>(zv[u]));
+                if (g == 0 && live && t + u < t1) y[(size_t)(t + u) * I + c] = from_float<T>((s + dsk * xv[u]) * silu_for<T>(zv[u]));
             }
         }
     }
     if (sum_dt) *sum_dt = total;
 }
 
+// a lane's K states from / to memory (16 bytes a time where the run is aligned)
+template <int K>
+__device__ __forceinline__ void state_io(float* st, float (&h)[K], int n_valid, bool store) {
+    if (K % 4 == 0 && n_valid == K && (reinterpret_cast<uintptr_t>(st) & 15) == 0) {
+#pragma unroll
+        for (int k = 0; k < K; k += 4) {
+            float4* p = reinterpret_cast<float4*>(st + k);
+            if (store) *p = make_float4(h[k], h[k + 1], h[k + 2], h[k + 3]);
+            else { const float4 v = *p; h[k] = v.x; h[k + 1] = v.y; h[k + 2] = v.z; h[k + 3] = v.w; }
+        }
+    } else {
+#pragma unroll
+        for (int k = 0; k < K; ++k) {
+            if (k < n_valid) { if (store) st[k] = h[k]; else h[k] = st[k]; }
+            else if (!store) h[k] = 0.f;
+        }
+    }
+}
+
 // ---- one pass: a block walks one request's rows (U = 1: every request brings one token)
 template <typename T, int K, int G, int U>
 __global__ void __launch_bounds__(128) selective_scan_kernel(
     T* __restrict__ y, const T* __restrict__ x, const T* __restrict__ proj, int proj_stride, const T* __restrict__ z,
-    int z_stride, const T* __restrict__ w_dt, const float* __restrict__ b_dt, const float* __restrict__ a_log,
+    int z_stride, const float* __restrict__ dt_raw, const float* __restrict__ b_dt, const float* __restrict__ a_log,
     const float* __restrict__ d_skip, float* __restrict__ state, const int* __restrict__ cu_q,
     const int* __restrict__ slot_ids, int I, int S, int R, int write_state, int num_slots, int* __restrict__ status) {
     pdl_trigger();
@@ -188,23 +177,15 @@ __global__ void __launch_bounds__(128) selective_scan_kernel(
     const int start = cu_q[seq], end = cu_q[seq + 1];
     if (end <= start) return;
     const int slot = zai_checked_slot(slot_ids[seq], num_slots, status);
-    float* st = state + ((size_t)slot * I + c) * S;
+    const int n_mine = max(min(S - g * K, K), 0);
+    float* st = state + ((size_t)slot * I + c) * S + g * K;
     float h[K], a[K];
+    state_io<K>(st, h, n_mine, false);
 #pragma unroll
-    for (int k = 0; k < K; ++k) {
-        const int n = g * K + k;
-        h[k] = n < S ? st[n] : 0.f;
-        a[k] = n < S ? -expf(a_log[(size_t)c * S + n]) : 0.f;
-    }
-    scan_walk<T, K, G, true, false, U>(h, a, start, end, c, g, live, y, x, proj, proj_stride, z, z_stride, w_dt + (size_t)c * R,
-                                    nullptr, b_dt[c], d_skip[c], I, S, R, nullptr);
-    if (write_state && live) {
-#pragma unroll
-        for (int k = 0; k < K; ++k) {
-            const int n = g * K + k;
-            if (n < S) st[n] = h[k];
-        }
-    }
+    for (int k = 0; k < K; ++k) a[k] = k < n_mine ? -expf(a_log[(size_t)c * S + g * K + k]) : 0.f;
+    scan_walk<T, K, G, true, U, false>(h, a, start, end, c, g, live, y, x, proj, proj_stride, z, z_stride, dt_raw, b_dt[c],
+                                       d_skip[c], I, S, R, nullptr);
+    if (write_state && live) state_io<K>(st, h, n_mine, true);
 }
 
 // ---- three passes.  ends [chunks, I, S]: a chunk's end state from zero, then (after pass 2) its start state;
@@ -217,29 +198,26 @@ __global__ void __launch_bounds__(128) selective_scan_chunk_kernel(
     int n_seqs, int Lc, int I, int S, int R) {
     pdl_trigger();
     pdl_wait();
-    int seq, t0, t1, last;
-    if (!zai_find_chunk(cu_q, n_seqs, Lc, blockIdx.x, seq, t0, t1, last)) return;
+    int seq, t0, t1;
+    if (!zai_find_chunk(cu_q, n_seqs, Lc, blockIdx.x, seq, t0, t1)) return;
     const int g = threadIdx.x % G;
     int c = blockIdx.y * (128 / G) + threadIdx.x / G;
     const bool live = c < I;
     if (!live) c = I - 1;
-    float* e = ends + ((size_t)blockIdx.x * I + c) * S;
+    const int n_mine = max(min(S - g * K, K), 0);
+    float* e = ends + ((size_t)blockIdx.x * I + c) * S + g * K;
     float h[K], a[K];
+    if (EMIT) state_io<K>(e, h, n_mine, false);
 #pragma unroll
     for (int k = 0; k < K; ++k) {
-        const int n = g * K + k;
-        h[k] = (EMIT && n < S) ? e[n] : 0.f;
-        a[k] = n < S ? -expf(a_log[(size_t)c * S + n]) : 0.f;
+        if (!EMIT) h[k] = 0.f;
+        a[k] = k < n_mine ? -expf(a_log[(size_t)c * S + g * K + k]) : 0.f;
     }
     float total = 0.f;
-    scan_walk<T, K, G, EMIT, true, ZAI_SCAN_PRE_U>(h, a, t0, t1, c, g, live, y, x, proj, proj_stride, z, z_stride, (const T*)nullptr, dt_raw,
-                                   b_dt[c], d_skip[c], I, S, R, &total);
+    scan_walk<T, K, G, EMIT, (K > 8 ? 2 : 4), true>(h, a, t0, t1, c, g, live, y, x, proj, proj_stride, z, z_stride, dt_raw,
+                                                    b_dt[c], d_skip[c], I, S, R, &total);
     if (!EMIT && live) {
-#pragma unroll
-        for (int k = 0; k < K; ++k) {
-            const int n = g * K + k;
-            if (n < S) e[n] = h[k];
-        }
+        state_io<K>(e, h, n_mine, true);
         if (g == 0) sums[(size_t)blockIdx.x * I + c] = total;
     }
 }
@@ -274,21 +252,20 @@ __global__ void selective_scan_carry_kernel(float* __restrict__ ends, const floa
 }
 
 template <typename T, int K, int G>
-static int launch_scan(void* y, const void* x, const void* proj, int proj_stride, const void* z, int z_stride, const void* w_dt,
+static int launch_scan(void* y, const void* x, const void* proj, int proj_stride, const void* z, int z_stride, const float* dt_raw,
                        const float* b_dt, const float* a_log, const float* d_skip, float* state, const int* cu_q,
                        const int* slot_ids, int n_seqs, int I, int S, int R, int write_state, int num_slots, int* status,
-                       float* ends, float* sums, const float* dt_raw, int chunk, int max_chunks, int single_tokens,
-                       cudaStream_t stream) {
+                       float* ends, float* sums, int chunk, int max_chunks, int single_tokens, cudaStream_t stream) {
     const int per_block = 128 / G;
     const unsigned cb = (unsigned)((I + per_block - 1) / per_block);
     if (cb > 65535) return ZAI_BAD_SIZE;
     if (single_tokens)
         return launch_pdl(selective_scan_kernel<T, K, G, 1>, dim3(n_seqs, cb), dim3(128), 0, stream, (T*)y, (const T*)x,
-                          (const T*)proj, proj_stride, (const T*)z, z_stride, (const T*)w_dt, b_dt, a_log, d_skip, state, cu_q,
-                          slot_ids, I, S, R, write_state, num_slots, status);
-    if (!ends || !dt_raw || chunk <= 0)
-        return launch_pdl(selective_scan_kernel<T, K, G, 4>, dim3(n_seqs, cb), dim3(128), 0, stream, (T*)y, (const T*)x,
-                          (const T*)proj, proj_stride, (const T*)z, z_stride, (const T*)w_dt, b_dt, a_log, d_skip, state, cu_q,
+                          (const T*)proj, proj_stride, (const T*)z, z_stride, dt_raw, b_dt, a_log, d_skip, state, cu_q, slot_ids,
+                          I, S, R, write_state, num_slots, status);
+    if (!ends || chunk <= 0)
+        return launch_pdl(selective_scan_kernel<T, K, G, (K > 8 ? 2 : 4)>, dim3(n_seqs, cb), dim3(128), 0, stream, (T*)y,
+                          (const T*)x, (const T*)proj, proj_stride, (const T*)z, z_stride, dt_raw, b_dt, a_log, d_skip, state, cu_q,
                           slot_ids, I, S, R, write_state, num_slots, status);
     int rc = launch_pdl(selective_scan_chunk_kernel<T, K, G, false>, dim3(max_chunks, cb), dim3(128), 0, stream, (T*)y,
                         (const T*)x, (const T*)proj, proj_stride, (const T*)z, z_stride, dt_raw, b_dt, a_log, d_skip, ends,
@@ -302,27 +279,27 @@ static int launch_scan(void* y, const void* x, const void* proj, int proj_stride
                       n_seqs, chunk, I, S, R);
 }
 
-// y [N, I]; x [N, I]; proj [N, proj_stride] (dt_in | B | C); z [N, z_stride]; w_dt [I, R]; state [slots, I, S].
-// With `ends` [max_chunks, I, S] and `sums` [max_chunks, I] (32-bit scratch), `dt_raw` [N, I] (the products
-// dt_in . w_dt^T in 32-bit, made by a matrix product beforehand) and chunk > 0 the step runs in three passes over
-// chunks of `chunk` rows; max_chunks >= the number of chunks of the step (N / chunk + n_seqs covers it).
+// y [N, I]; x [N, I]; proj [N, proj_stride] (dt_in | B | C, of which B and C are read here); z [N, z_stride];
+// dt_raw [N, I]: the products dt_in . w_dt^T in 32-bit (a matrix product made beforehand); state [slots, I, S].
+// With `ends` [max_chunks, I, S] and `sums` [max_chunks, I] (32-bit scratch) and chunk > 0 the step runs in three
+// passes over chunks of `chunk` rows; max_chunks >= the number of chunks of the step (N / chunk + n_seqs covers it).
 // single_tokens: every request brings one row (a leaner kernel).
 ZAI_API int zai_selective_scan(void* y, const void* x, const void* proj, int proj_stride, const void* z, int z_stride, int dtype,
-                               const void* w_dt, const float* b_dt, const float* a_log, const float* d_skip, float* state,
+                               const float* dt_raw, const float* b_dt, const float* a_log, const float* d_skip, float* state,
                                const int* cu_q, const int* slot_ids, int N, int n_seqs, int I, int S, int R, int write_state,
-                               int num_slots, int* status, float* ends, float* sums, const float* dt_raw, int chunk,
-                               int max_chunks, int single_tokens, cudaStream_t stream) {
+                               int num_slots, int* status, float* ends, float* sums, int chunk, int max_chunks,
+                               int single_tokens, cudaStream_t stream) {
     if (N <= 0 || n_seqs <= 0) return ZAI_OK;
-    if (I < 1 || S < 1 || S > 256 || R < 1) return ZAI_BAD_SIZE;
-#define ZAI_SCAN(KK, GG) ZAI_DISPATCH(dtype, return launch_scan<T, KK, GG>(y, x, proj, proj_stride, z, z_stride, w_dt, b_dt, a_log, \
-        d_skip, state, cu_q, slot_ids, n_seqs, I, S, R, write_state, num_slots, status, ends, sums, dt_raw, chunk, max_chunks, \
+    if (I < 1 || S < 1 || S > 256 || R < 1 || !dt_raw) return ZAI_BAD_SIZE;
+#define ZAI_SCAN(KK, GG) ZAI_DISPATCH(dtype, return launch_scan<T, KK, GG>(y, x, proj, proj_stride, z, z_stride, dt_raw, b_dt, a_log, \
+        d_skip, state, cu_q, slot_ids, n_seqs, I, S, R, write_state, num_slots, status, ends, sums, chunk, max_chunks, \
         single_tokens && N == n_seqs, stream))
-    if (S <= 4) ZAI_SCAN(1, 4);
-    if (S <= 8) ZAI_SCAN(2, 4);
-    if (S <= 16) ZAI_SCAN(4, 4);
-    if (S <= 32) ZAI_SCAN(8, 4);
-    if (S <= 64) ZAI_SCAN(8, 8);
-    if (S <= 128) ZAI_SCAN(8, 16);
-    ZAI_SCAN(8, 32);
+    if (S <= 4) ZAI_SCAN(4, 1);
+    if (S <= 8) ZAI_SCAN(8, 1);
+    if (S <= 16) ZAI_SCAN(16, 1);
+    if (S <= 32) ZAI_SCAN(16, 2);
+    if (S <= 64) ZAI_SCAN(16, 4);
+    if (S <= 128) ZAI_SCAN(16, 8);
+    ZAI_SCAN(16, 16);
 #undef ZAI_SCAN
 }

@@ -37,7 +37,7 @@ _SIGNATURES = {
                    "zai_weighted_sum": [_P, _P, _P, _I, _F, _F, ctypes.c_longlong, _P]},
     "causal_conv": {"zai_causal_conv": [_P, _I, _P, _I, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P]},
     "selective_scan": {"zai_selective_scan": [_P, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I,
-                                              _I, _P, _P, _P, _P, _I, _I, _I, _P]},
+                                              _I, _P, _P, _P, _I, _I, _I, _P]},
     "min_gru": {"zai_min_gru": [_P, _P, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _I, _I, _P]},
     "gated_delta": {
         "zai_delta_prepare": [_P, _P, _P, _I, _P, _P, _I, _I, _P, _P, _I, _I, _I, _I, _F, _P],
@@ -1015,14 +1015,13 @@ def selective_scan(x, proj, z, w_dt, b_dt, a_log, d_skip, state, step, dt_rank, 
     chunk, max_chunks = _scan_chunks(step, N)
     ends = torch.empty((max_chunks, I, S), dtype=torch.float32, device=x.device) if chunk else None
     sums = torch.empty((max_chunks, I), dtype=torch.float32, device=x.device) if chunk else None
-    # long portions: the step sizes' products for all rows as one matrix product (32-bit result)
-    dt_raw = _library_product(proj[:, :R], w_dt, torch.float32) if chunk else None
+    # the step sizes' products dt_in . w_dt^T for all rows as one matrix product with a 32-bit result
+    dt_raw = linear(proj[:, :R], w_dt, out_dtype=torch.float32)
     _check(_fn("selective_scan", "zai_selective_scan")(
-        _ptr(y), _ptr(x), pp, ps, zp, zs, _dt(x), _ptr(w_dt), _ptr(b_dt), _ptr(a_log), _ptr(d_skip), _ptr(state),
+        _ptr(y), _ptr(x), pp, ps, zp, zs, _dt(x), _ptr(dt_raw), _ptr(b_dt), _ptr(a_log), _ptr(d_skip), _ptr(state),
         _ptr(step.cu_q), _ptr(step.slot_ids), N, step.n_seqs, I, S, R, int(bool(write_state)), state.shape[0],
-        _status_ptr(x.device), _ptr(ends), _ptr(sums), _ptr(dt_raw), chunk, max_chunks, int(bool(step.decode_only)), _stream()),
-        "selective_scan",
-        3 if chunk else 1)
+        _status_ptr(x.device), _ptr(ends), _ptr(sums), chunk, max_chunks, int(bool(step.decode_only)), _stream()),
+        "selective_scan", 3 if chunk else 1)
     return y
 
 
