@@ -219,6 +219,8 @@ ZAI_API int zai_gated_delta(float* o_out, const float* qk, const float* bg, cons
     if (D < 1 || D > 256 || V < 1 || G < 1 || H % G != 0 || H > 65535 || V > 65535 * 16) return ZAI_BAD_SIZE;
 #define ZAI_DELTA(DPV, PV) ZAI_DISPATCH(dtype, return launch_delta<T, DPV, PV>(o_out, qk, bg, v_in, v_stride, state, cu_q, slot_ids, \
         n_seqs, H, G, D, V, write_state, num_slots, status, stream))
+    // four lanes a column (eight for the largest heads): measured against two and one (fewer exchanges, longer
+    // chains of multiply-adds a lane), four was the fastest or level at 64-wide heads
     if (D <= 16) ZAI_DELTA(4, 4);
     if (D <= 32) ZAI_DELTA(8, 4);
     if (D <= 64) ZAI_DELTA(16, 4);

@@ -961,13 +961,16 @@ def weighted_sum(a, b, wa, wb):
 CHUNKED_SCAN_MIN_ROWS = 256     # steps with prompt portions of this many rows or more run the linear recurrences in chunks
 
 
-def _scan_chunks(step, n_rows):
+def _scan_chunks(step, n_rows, channel_blocks=16):
     """(rows per chunk, upper bound of the chunks) for a recurrence that is linear in its state, or (0, 0) where
-    the rows of each request are walked in one pass: steps of single tokens and small steps.  Both depend only on
-    the step's row and request counts, which a captured step shape keeps."""
+    the rows of each request are walked in one pass: steps of single tokens and small steps.  Chunks are as long
+    as still gives about a thousand blocks (chunks x blocks of channels), between 16 and 256 rows.  Both numbers
+    depend only on the step's row and request counts, which a captured step shape keeps."""
     if step.decode_only or n_rows < CHUNKED_SCAN_MIN_ROWS:
         return 0, 0
-    chunk = 64 if n_rows <= 8192 else 256
+    chunk = 256
+    while chunk > 16 and (n_rows // chunk) * channel_blocks < 1024:
+        chunk //= 2
     return chunk, n_rows // chunk + step.n_seqs
 
 
@@ -1012,7 +1015,7 @@ def selective_scan(x, proj, z, w_dt, b_dt, a_log, d_skip, state, step, dt_rank, 
     if state.dtype != torch.float32 or tuple(state.shape[1:]) != (I, S):
         raise KernelError("the scan state is 32-bit [slots, inner, state]")
     y = torch.empty((N, I), dtype=x.dtype, device=x.device)
-    chunk, max_chunks = _scan_chunks(step, N)
+    chunk, max_chunks = _scan_chunks(step, N, -(-I // (128 if S <= 16 else 64)))
     ends = torch.empty((max_chunks, I, S), dtype=torch.float32, device=x.device) if chunk else None
     sums = torch.empty((max_chunks, I), dtype=torch.float32, device=x.device) if chunk else None
     # the step sizes' products dt_in . w_dt^T for all rows as one matrix product with a 32-bit result
@@ -1035,7 +1038,7 @@ def min_gru(zxg, b_z, b_x, state, step, write_state=True):
     if state.dtype != torch.float32 or tuple(state.shape[1:]) != (W,):
         raise KernelError("the recurrence's state is 32-bit [slots, width]")
     out = torch.empty((N, W), dtype=zxg.dtype, device=zxg.device)
-    chunk, max_chunks = _scan_chunks(step, N)
+    chunk, max_chunks = _scan_chunks(step, N, -(-W // 128))
     ends = torch.empty((2, max_chunks, W), dtype=torch.float32, device=zxg.device) if chunk else None
     _check(_fn("min_gru", "zai_min_gru")(_ptr(out), p, stride, _dt(zxg), _ptr(b_z), _ptr(b_x), _ptr(state), _ptr(step.cu_q),
                                          _ptr(step.slot_ids), N, step.n_seqs, W, int(bool(write_state)), state.shape[0],
