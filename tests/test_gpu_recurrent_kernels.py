@@ -54,7 +54,7 @@ def test_causal_conv_spans_and_state(dtype, C, L, bias, act):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("I,S,R", [(96, 24, 16), (70, 3, 5), (33, 16, 1), (40, 40, 7), (20, 100, 9), (12, 200, 3)])
+@pytest.mark.parametrize("I,S,R", [(96, 20, 12), (70, 3, 5), (33, 16, 1), (40, 40, 7), (20, 100, 9), (12, 200, 3)])
 def test_selective_scan(dtype, I, S, R):
     o = ops()
     g = torch.Generator().manual_seed(6)
@@ -78,7 +78,7 @@ def test_selective_scan(dtype, I, S, R):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("W", [224, 70, 1, 130])
+@pytest.mark.parametrize("W", [200, 70, 1, 130])
 def test_min_gru(dtype, W):
     o = ops()
     g = torch.Generator().manual_seed(7)
@@ -96,7 +96,7 @@ def test_min_gru(dtype, W):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("H,G,D,V", [(6, 3, 32, 64), (2, 2, 16, 24), (3, 1, 40, 33), (4, 2, 64, 128), (2, 1, 128, 48),
+@pytest.mark.parametrize("H,G,D,V", [(6, 2, 32, 40), (2, 2, 16, 24), (3, 1, 40, 33), (4, 2, 64, 128), (2, 1, 128, 48),
                                      (1, 1, 200, 20), (2, 1, 8, 70)])
 def test_gated_delta(dtype, H, G, D, V):
     o = ops()
@@ -170,7 +170,7 @@ def test_norm_of_the_pending_term(dtype, N, H):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("H,G,D,Dv", [(4, 2, 16, 16), (3, 1, 32, 48), (2, 2, 40, 24), (8, 1, 64, 64)])
+@pytest.mark.parametrize("H,G,D,Dv", [(4, 2, 16, 16), (3, 1, 32, 48), (2, 2, 40, 24), (6, 2, 64, 64)])
 @pytest.mark.parametrize("normed", [True, False])
 def test_value_norm_and_padding(dtype, H, G, D, Dv, normed):
     o = ops()

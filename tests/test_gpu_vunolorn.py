@@ -145,3 +145,36 @@ def test_greedy_generation_through_the_entry_point(models, name, dtype):
             slack = 1e-3 if dtype == "float32" else 8e-2 * float(row.abs().max())
             assert float(row.max() - row[tok]) <= slack, f"{dtype}: token {i} of a request is not the plain implementation's choice"
     assert eng.stats()["slots_used"] == 0
+
+
+def test_command_line_generates_and_samples(models, tmp_path):
+    """The command line with a Vunolorn model: random weights written from a config.json, greedy tokens equal to the
+    plain implementation's choice, sampled tokens reproducible, the kernel-class profile printed."""
+    import json
+    import os
+    import subprocess
+    import sys
+    cfg_path = tmp_path / "cfg.json"
+    cfg_path.write_text(json.dumps(ALL["A"][0]))
+    d = str(tmp_path / "m")
+    exe = [sys.executable, os.path.join(traces.ROOT, "bin", "zig-ai-engine")]
+    base = exe + ["-m", d, "--prompt", "5,17,3,90,41", "-n", "10", "--dtype", "float32", "--page-size", "8"]
+    out = subprocess.run(base + ["--random-weights", str(cfg_path), "--seed", "7", "--temperature", "0"],
+                         capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-2000:]
+    assert "Vunolorn" in out.stdout
+    line = [ln for ln in out.stdout.splitlines() if ln.startswith("[0]")][0]
+    toks = [int(t) for t in line.split(")")[1].split()]
+    assert len(toks) == 10
+    c, W = P.read_config(d), P.read_weights(d)
+    logits = P.forward(c, W, [5, 17, 3, 90, 41] + toks)
+    for i, tok in enumerate(toks):
+        row = logits[4 + i]
+        assert float(row.max() - row[tok]) < 1e-3
+    sampled = [subprocess.run(base + ["--temperature", "0.9", "--top-k", "20", "--top-p", "0.9", "--repetition-penalty", "1.2",
+                                      "--seed", "11", "-np", "2", "--profile"], capture_output=True, text=True, timeout=600)
+               for _ in range(2)]
+    assert all(r.returncode == 0 for r in sampled), sampled[0].stderr[-2000:]
+    pick = lambda r: [ln for ln in r.stdout.splitlines() if ln.startswith("[0]") or ln.startswith("[1]")]
+    assert pick(sampled[0]) == pick(sampled[1]) and len(pick(sampled[0])) == 2
+    assert "recurrence" in sampled[0].stdout

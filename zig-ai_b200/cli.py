@@ -40,7 +40,7 @@ def parse_ids(text: str):
 
 
 def build_parser() -> argparse.ArgumentParser:
-    ap = argparse.ArgumentParser(prog="zig-ai-engine", description="LFM2 inference on one B200")
+    ap = argparse.ArgumentParser(prog="zig-ai-engine", description="inference on one B200 for the registered architectures (LFM2, Vunolorn)")
     ap.add_argument("-m", "--model", help="model folder (config.json, model.safetensors)")
     ap.add_argument("--prompt", default=None, help="token ids, e.g. \"1,2,3\"")
     ap.add_argument("--prompt-file", default=None, help="file with one prompt (token ids) per line")
