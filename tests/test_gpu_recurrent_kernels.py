@@ -15,6 +15,7 @@ DTYPES = [torch.float32, torch.bfloat16]
 # the last two are long enough for the passes over chunks of rows (chunks that end inside and at a request's end,
 # a request shorter than a chunk, one of exactly two chunks)
 STEPS = ([1, 3, 4, 11, 1], [5, 1, 1, 2, 9], [1, 1, 1, 1, 1], [2, 37, 1, 1, 6], [200, 1, 63, 128, 70], [64, 65, 300, 2, 1])
+MANY_SINGLES = [1] * 20           # more single tokens than the one-kernel paths for few requests take
 
 
 def ops():
@@ -78,6 +79,27 @@ def test_selective_scan(dtype, I, S, R):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+def test_selective_scan_single_tokens_aligned_rows(dtype):
+    """A step of single tokens sums the step size's product itself, 16 bytes a load where the rows allow it."""
+    o = ops()
+    g = torch.Generator().manual_seed(13)
+    I, S, R = 72, 16, 32
+    w_dt = (torch.randn(I, R, generator=g) * 0.5).to(dtype).cuda()
+    b_dt, a_log, d = (torch.randn(I, generator=g) * 0.5).cuda(), (torch.randn(I, S, generator=g) * 0.5).cuda(), torch.randn(I, generator=g).cuda()
+    state_a = torch.randn(6, I, S, generator=g).cuda()
+    state_b = state_a.clone()
+    for _ in range(3):
+        step = make_step(o, dtype, [3] * 5, [1] * 5, 8, 64, 5)
+        x = torch.randn(5, I, generator=g).to(dtype).cuda()
+        proj = torch.randn(5, R + 2 * S, generator=g).to(dtype).cuda()
+        z = torch.randn(5, I, generator=g).to(dtype).cuda()
+        ya = o.selective_scan(x, proj, z, w_dt, b_dt, a_log, d, state_a, step, R, True)
+        yb = ref_ops.selective_scan(x, proj, z, w_dt, b_dt, a_log, d, state_b, step, R, True)
+        assert torch.allclose(ya.float(), yb.float(), **tol(dtype))
+        assert torch.allclose(state_a, state_b, atol=1e-4, rtol=1e-4)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("W", [200, 70, 1, 130])
 def test_min_gru(dtype, W):
     o = ops()
@@ -103,11 +125,11 @@ def test_gated_delta(dtype, H, G, D, V):
     g = torch.Generator().manual_seed(8)
     a_log, dt_bias = torch.randn(H, generator=g).cuda() * 0.5, torch.randn(H, generator=g).cuda() * 0.5
     norm_w = (1 + 0.1 * torch.randn(V, generator=g)).cuda()
-    state_a = (torch.randn(6, H, D, V, generator=g) * 0.3).cuda()
+    state_a = (torch.randn(22, H, D, V, generator=g) * 0.3).cuda()
     state_b = state_a.clone()
     cols = 2 * G * D + H * V
-    for q_lens in STEPS:
-        step = make_step(o, dtype, [3] * 5, q_lens, 8, 256, 5)
+    for q_lens in STEPS + (MANY_SINGLES,):
+        step = make_step(o, dtype, [3] * len(q_lens), q_lens, 8, 256, 5)
         N = sum(q_lens)
         qkv = torch.randn(N, cols, generator=g).to(dtype).cuda()
         rest = torch.randn(N, H * V + 2 * H, generator=g).to(dtype).cuda()

@@ -3,7 +3,8 @@
 //   S <- g S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q
 //
 // (the read-out sees the token's own write), with q and k unit vectors per head (q also times D^-1/2),
-// beta = sigmoid(b), g = exp(-exp(A_log) softplus(a + dt_bias)).  Three kernels:
+// beta = sigmoid(b), g = exp(-exp(A_log) softplus(a + dt_bias)).  A step of single tokens is one kernel (a block per
+// request and head does all of it); steps with portions run three kernels:
 //   * prepare: unit norms, beta and g for every row of the step, all 32-bit;
 //   * the recurrence: the columns of S are independent, so a block owns some columns of one head of one
 //     request and walks the request's rows in order; P lanes of a warp share a column, each with DP of
@@ -192,6 +193,109 @@ __global__ void gated_rmsnorm_kernel(T* __restrict__ out, const float* __restric
         const float gv = to_float(grow[d]);
         out[(size_t)item * V + d] = from_float<T>(src[d] * inv * (w ? w[d] : 1.f) * (gv / (1.f + expf(-gv))));
     }
+}
+
+// ---- a step of single tokens in one kernel: unit norms, beta and g, the state's update and read-out and the output
+// norm for one head of one request per block (all V columns: P lanes a column, so P * V threads, at most 1024)
+template <typename T, int DP, int P>
+__global__ void __launch_bounds__(1024) gated_delta_single_kernel(
+    T* __restrict__ out, const T* __restrict__ qkv, int qkv_stride, const T* __restrict__ b_in, const T* __restrict__ a_in,
+    int ba_stride, const T* __restrict__ gate, int gate_stride, const float* __restrict__ a_log,
+    const float* __restrict__ dt_bias, const float* __restrict__ norm_w, float eps, float unit_eps, float* __restrict__ state,
+    const int* __restrict__ slot_ids, int H, int G, int D, int V, int write_state, int num_slots, int* __restrict__ status) {
+    extern __shared__ float sm[];                      // q [D], k [D], 33 for the block's sum
+    float* qs = sm;
+    float* ks = sm + D;
+    float* red = sm + 2 * D;
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x, h = blockIdx.y, kvh = h / (H / G);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
+    const T* row = qkv + (size_t)t * qkv_stride;
+    for (int item = warp; item < 2; item += nwarp) {                  // 0: q, 1: k of this head's q/k head
+        const T* src = row + (size_t)(item * G + kvh) * D;
+        float ss = 0.f;
+        for (int d = lane; d < D; d += 32) {
+            const float v = to_float(src[d]);
+            ss += v * v;
+        }
+        ss = warp_sum(ss);
+        const float inv = rsqrtf(ss + unit_eps) * (item == 0 ? rsqrtf((float)D) : 1.f);
+        float* dst = item == 0 ? qs : ks;
+        for (int d = lane; d < D; d += 32) dst[d] = to_float(src[d]) * inv;
+    }
+    __syncthreads();
+    const float beta = 1.f / (1.f + expf(-to_float(b_in[(size_t)t * ba_stride + h])));
+    const float g = expf(-expf(a_log[h]) * softplus_f(to_float(a_in[(size_t)t * ba_stride + h]) + dt_bias[h]));
+    const int p = threadIdx.x % P, d0 = p * DP;
+    int j = threadIdx.x / P;
+    const bool live = j < V;
+    if (!live) j = V - 1;
+    const int slot = zai_checked_slot(slot_ids[t], num_slots, status);
+    float* st = state + (((size_t)slot * H + h) * D) * V + j;
+    float S[DP];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < DP; ++i) {
+        S[i] = d0 + i < D ? st[(size_t)(d0 + i) * V] * g : 0.f;
+        dot += d0 + i < D ? S[i] * ks[d0 + i] : 0.f;
+    }
+#pragma unroll
+    for (int o = P / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+    const float u = beta * (to_float(row[(size_t)2 * G * D + (size_t)h * V + j]) - dot);
+    float o_j = 0.f;
+#pragma unroll
+    for (int i = 0; i < DP; ++i) {
+        if (d0 + i < D) {
+            S[i] += ks[d0 + i] * u;
+            o_j += S[i] * qs[d0 + i];
+            if (write_state && live) st[(size_t)(d0 + i) * V] = S[i];
+        }
+    }
+#pragma unroll
+    for (int o = P / 2; o > 0; o >>= 1) o_j += __shfl_xor_sync(0xffffffffu, o_j, o);
+    const float ss = block_sum((p == 0 && live) ? o_j * o_j : 0.f, red);
+    const float inv = rsqrtf(ss / (float)V + eps);
+    if (p == 0 && live) {
+        const float gv = to_float(gate[(size_t)t * gate_stride + (size_t)h * V + j]);
+        out[((size_t)t * H + h) * V + j] = from_float<T>(o_j * inv * (norm_w ? norm_w[j] : 1.f) * (gv / (1.f + expf(-gv))));
+    }
+}
+
+template <typename T, int DP, int P>
+static int launch_delta_single(void* out, const void* qkv, int qkv_stride, const void* b_in, const void* a_in, int ba_stride,
+                               const void* gate, int gate_stride, const float* a_log, const float* dt_bias, const float* norm_w,
+                               float eps, float unit_eps, float* state, const int* slot_ids, int B, int H, int G, int D, int V,
+                               int write_state, int num_slots, int* status, cudaStream_t stream) {
+    const int threads = ((P * V + 31) / 32) * 32;
+    if (threads > 1024) return ZAI_BAD_SIZE;
+    return launch_pdl(gated_delta_single_kernel<T, DP, P>, dim3(B, H), dim3(threads), (size_t)(2 * D + 33) * sizeof(float), stream,
+                      (T*)out, (const T*)qkv, qkv_stride, (const T*)b_in, (const T*)a_in, ba_stride, (const T*)gate, gate_stride,
+                      a_log, dt_bias, norm_w, eps, unit_eps, state, slot_ids, H, G, D, V, write_state, num_slots, status);
+}
+
+// 1 if a step of single tokens with these sizes can run as the one kernel above
+ZAI_API int zai_gated_delta_single_supports(int D, int V) {
+    const int P = D <= 128 ? 4 : 8;
+    return D >= 1 && D <= 256 && V >= 1 && ((P * V + 31) / 32) * 32 <= 1024;
+}
+
+// out [B, H*V] in the model's dtype; qkv [B, qkv_stride] (q heads, k heads, v heads, after their convolutions);
+// b_in, a_in [B, ba_stride]; gate [B, gate_stride]; state [slots, H, D, V]; row i belongs to slot_ids[i]
+ZAI_API int zai_gated_delta_single(void* out, const void* qkv, int qkv_stride, const void* b_in, const void* a_in, int ba_stride,
+                                   const void* gate, int gate_stride, int dtype, const float* a_log, const float* dt_bias,
+                                   const float* norm_w, float eps, float unit_eps, float* state, const int* slot_ids, int B, int H,
+                                   int G, int D, int V, int write_state, int num_slots, int* status, cudaStream_t stream) {
+    if (B <= 0) return ZAI_OK;
+    if (!zai_gated_delta_single_supports(D, V) || G < 1 || H % G != 0 || H > 65535) return ZAI_BAD_SIZE;
+#define ZAI_DELTA1(DPV, PV) ZAI_DISPATCH(dtype, return launch_delta_single<T, DPV, PV>(out, qkv, qkv_stride, b_in, a_in, ba_stride, \
+        gate, gate_stride, a_log, dt_bias, norm_w, eps, unit_eps, state, slot_ids, B, H, G, D, V, write_state, num_slots, status, stream))
+    if (D <= 16) ZAI_DELTA1(4, 4);
+    if (D <= 32) ZAI_DELTA1(8, 4);
+    if (D <= 64) ZAI_DELTA1(16, 4);
+    if (D <= 128) ZAI_DELTA1(32, 4);
+    ZAI_DELTA1(32, 8);
+#undef ZAI_DELTA1
 }
 
 ZAI_API int zai_delta_prepare(float* qk_out, float* bg_out, const void* qkv, int qkv_stride, const void* b_in, const void* a_in,

@@ -77,11 +77,34 @@ __device__ __forceinline__ void prefetch_l1(const void* p) { asm volatile("prefe
 // the same addresses for every lane of a warp).  `dt_raw` [N, I] holds the step sizes' products dt_in . Wdt^T in
 // 32-bit (a matrix product made beforehand).  EMIT: writes y.  U rows are in flight together.  PREFETCH: the rows
 // are first asked into L1 (one trip to memory for a chunk, not one per group of rows).
+// dt_in . wrow over R terms, split over the G lanes of the channel (16 bytes a load where rows are aligned)
+template <typename T, int G>
+__device__ __forceinline__ float step_size_product(const T* __restrict__ wrow, const T* __restrict__ prow, int R, int g, bool vec) {
+    float s = 0.f;
+    if (sizeof(T) == 2 && vec) {
+        for (int r = g * 8; r < R; r += G * 8) {
+            const uint4 wv = *reinterpret_cast<const uint4*>(wrow + r), pv = *reinterpret_cast<const uint4*>(prow + r);
+            const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wv);
+            const __nv_bfloat162* pp = reinterpret_cast<const __nv_bfloat162*>(&pv);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 a = __bfloat1622float2(wp[e]), b = __bfloat1622float2(pp[e]);
+                s += a.x * b.x + a.y * b.y;
+            }
+        }
+    } else {
+        for (int r = g; r < R; r += G) s += to_float(wrow[r]) * to_float(prow[r]);
+    }
+#pragma unroll
+    for (int o = G / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    return s;
+}
+
 template <typename T, int K, int G, bool EMIT, int U, bool PREFETCH>
 __device__ __forceinline__ void scan_walk(float (&h)[K], const float (&a)[K], int t0, int t1, int c, int g, bool live,
                                           T* __restrict__ y, const T* __restrict__ x, const T* __restrict__ proj, int proj_stride,
-                                          const T* __restrict__ z, int z_stride, const float* __restrict__ dt_raw, float bias,
-                                          float dsk, int I, int S, int R, float* sum_dt) {
+                                          const T* __restrict__ z, int z_stride, const float* __restrict__ dt_raw,
+                                          const T* __restrict__ wrow, float bias, float dsk, int I, int S, int R, float* sum_dt) {
     if (PREFETCH) {
         const int c0 = blockIdx.y * (128 / G);
         for (int tt = t0 + threadIdx.x; tt < t1; tt += 128) {
@@ -106,7 +129,12 @@ __device__ __forceinline__ void scan_walk(float (&h)[K], const float (&a)[K], in
             const bool on = t + u < t1;
             const int tt = on ? t + u : t;
             const T* p = proj + (size_t)tt * proj_stride + R + g * K;
-            dt[u] = on ? dt_raw[(size_t)tt * I + c] : 0.f;
+            if (dt_raw) {
+                dt[u] = on ? dt_raw[(size_t)tt * I + c] : 0.f;
+            } else {                                   // (single-token steps: the product is summed here, no launch for it)
+                const bool vec8 = ((proj_stride | R) & 7) == 0 && ((reinterpret_cast<uintptr_t>(proj) | reinterpret_cast<uintptr_t>(wrow)) & 15) == 0;
+                dt[u] = step_size_product<T, G>(wrow, proj + (size_t)tt * proj_stride, R, g, vec8);
+            }
             xv[u] = on ? to_float(x[(size_t)tt * I + c]) : 0.f;
             zv[u] = (EMIT && on) ? to_float(z[(size_t)tt * z_stride + c]) : 0.f;
             load_run<K>(p, bv[u], on ? n_mine : 0, vec);
@@ -164,8 +192,8 @@ __device__ __forceinline__ void state_io(float* st, float (&h)[K], int n_valid, 
 template <typename T, int K, int G, int U>
 __global__ void __launch_bounds__(128) selective_scan_kernel(
     T* __restrict__ y, const T* __restrict__ x, const T* __restrict__ proj, int proj_stride, const T* __restrict__ z,
-    int z_stride, const float* __restrict__ dt_raw, const float* __restrict__ b_dt, const float* __restrict__ a_log,
-    const float* __restrict__ d_skip, float* __restrict__ state, const int* __restrict__ cu_q,
+    int z_stride, const float* __restrict__ dt_raw, const T* __restrict__ w_dt, const float* __restrict__ b_dt,
+    const float* __restrict__ a_log, const float* __restrict__ d_skip, float* __restrict__ state, const int* __restrict__ cu_q,
     const int* __restrict__ slot_ids, int I, int S, int R, int write_state, int num_slots, int* __restrict__ status) {
     pdl_trigger();
     pdl_wait();
@@ -183,8 +211,8 @@ __global__ void __launch_bounds__(128) selective_scan_kernel(
     state_io<K>(st, h, n_mine, false);
 #pragma unroll
     for (int k = 0; k < K; ++k) a[k] = k < n_mine ? -expf(a_log[(size_t)c * S + g * K + k]) : 0.f;
-    scan_walk<T, K, G, true, U, false>(h, a, start, end, c, g, live, y, x, proj, proj_stride, z, z_stride, dt_raw, b_dt[c],
-                                       d_skip[c], I, S, R, nullptr);
+    scan_walk<T, K, G, true, U, false>(h, a, start, end, c, g, live, y, x, proj, proj_stride, z, z_stride, dt_raw,
+                                       w_dt + (size_t)c * R, b_dt[c], d_skip[c], I, S, R, nullptr);
     if (write_state && live) state_io<K>(st, h, n_mine, true);
 }
 
@@ -215,7 +243,7 @@ __global__ void __launch_bounds__(128) selective_scan_chunk_kernel(
     }
     float total = 0.f;
     scan_walk<T, K, G, EMIT, (K > 8 ? 2 : 4), true>(h, a, t0, t1, c, g, live, y, x, proj, proj_stride, z, z_stride, dt_raw,
-                                                    b_dt[c], d_skip[c], I, S, R, &total);
+                                                    (const T*)nullptr, b_dt[c], d_skip[c], I, S, R, &total);
     if (!EMIT && live) {
         state_io<K>(e, h, n_mine, true);
         if (g == 0) sums[(size_t)blockIdx.x * I + c] = total;
@@ -253,7 +281,7 @@ __global__ void selective_scan_carry_kernel(float* __restrict__ ends, const floa
 
 template <typename T, int K, int G>
 static int launch_scan(void* y, const void* x, const void* proj, int proj_stride, const void* z, int z_stride, const float* dt_raw,
-                       const float* b_dt, const float* a_log, const float* d_skip, float* state, const int* cu_q,
+                       const void* w_dt, const float* b_dt, const float* a_log, const float* d_skip, float* state, const int* cu_q,
                        const int* slot_ids, int n_seqs, int I, int S, int R, int write_state, int num_slots, int* status,
                        float* ends, float* sums, int chunk, int max_chunks, int single_tokens, cudaStream_t stream) {
     const int per_block = 128 / G;
@@ -261,12 +289,13 @@ static int launch_scan(void* y, const void* x, const void* proj, int proj_stride
     if (cb > 65535) return ZAI_BAD_SIZE;
     if (single_tokens)
         return launch_pdl(selective_scan_kernel<T, K, G, 1>, dim3(n_seqs, cb), dim3(128), 0, stream, (T*)y, (const T*)x,
-                          (const T*)proj, proj_stride, (const T*)z, z_stride, dt_raw, b_dt, a_log, d_skip, state, cu_q, slot_ids,
-                          I, S, R, write_state, num_slots, status);
+                          (const T*)proj, proj_stride, (const T*)z, z_stride, dt_raw, (const T*)w_dt, b_dt, a_log, d_skip, state,
+                          cu_q, slot_ids, I, S, R, write_state, num_slots, status);
+    if (!dt_raw) return ZAI_BAD_SIZE;
     if (!ends || chunk <= 0)
         return launch_pdl(selective_scan_kernel<T, K, G, (K > 8 ? 2 : 4)>, dim3(n_seqs, cb), dim3(128), 0, stream, (T*)y,
-                          (const T*)x, (const T*)proj, proj_stride, (const T*)z, z_stride, dt_raw, b_dt, a_log, d_skip, state, cu_q,
-                          slot_ids, I, S, R, write_state, num_slots, status);
+                          (const T*)x, (const T*)proj, proj_stride, (const T*)z, z_stride, dt_raw, (const T*)w_dt, b_dt, a_log, d_skip,
+                          state, cu_q, slot_ids, I, S, R, write_state, num_slots, status);
     int rc = launch_pdl(selective_scan_chunk_kernel<T, K, G, false>, dim3(max_chunks, cb), dim3(128), 0, stream, (T*)y,
                         (const T*)x, (const T*)proj, proj_stride, (const T*)z, z_stride, dt_raw, b_dt, a_log, d_skip, ends,
                         sums, cu_q, n_seqs, chunk, I, S, R);
@@ -280,18 +309,20 @@ static int launch_scan(void* y, const void* x, const void* proj, int proj_stride
 }
 
 // y [N, I]; x [N, I]; proj [N, proj_stride] (dt_in | B | C, of which B and C are read here); z [N, z_stride];
-// dt_raw [N, I]: the products dt_in . w_dt^T in 32-bit (a matrix product made beforehand); state [slots, I, S].
+// dt_raw [N, I]: the products dt_in . w_dt^T in 32-bit (a matrix product made beforehand), or null in a step of single
+// tokens, which then sums them from w_dt [I, R] itself; state [slots, I, S].
 // With `ends` [max_chunks, I, S] and `sums` [max_chunks, I] (32-bit scratch) and chunk > 0 the step runs in three
 // passes over chunks of `chunk` rows; max_chunks >= the number of chunks of the step (N / chunk + n_seqs covers it).
 // single_tokens: every request brings one row (a leaner kernel).
 ZAI_API int zai_selective_scan(void* y, const void* x, const void* proj, int proj_stride, const void* z, int z_stride, int dtype,
-                               const float* dt_raw, const float* b_dt, const float* a_log, const float* d_skip, float* state,
+                               const float* dt_raw, const void* w_dt, const float* b_dt, const float* a_log, const float* d_skip,
+                               float* state,
                                const int* cu_q, const int* slot_ids, int N, int n_seqs, int I, int S, int R, int write_state,
                                int num_slots, int* status, float* ends, float* sums, int chunk, int max_chunks,
                                int single_tokens, cudaStream_t stream) {
     if (N <= 0 || n_seqs <= 0) return ZAI_OK;
-    if (I < 1 || S < 1 || S > 256 || R < 1 || !dt_raw) return ZAI_BAD_SIZE;
-#define ZAI_SCAN(KK, GG) ZAI_DISPATCH(dtype, return launch_scan<T, KK, GG>(y, x, proj, proj_stride, z, z_stride, dt_raw, b_dt, a_log, \
+    if (I < 1 || S < 1 || S > 256 || R < 1 || (!dt_raw && !w_dt)) return ZAI_BAD_SIZE;
+#define ZAI_SCAN(KK, GG) ZAI_DISPATCH(dtype, return launch_scan<T, KK, GG>(y, x, proj, proj_stride, z, z_stride, dt_raw, w_dt, b_dt, a_log, \
         d_skip, state, cu_q, slot_ids, n_seqs, I, S, R, write_state, num_slots, status, ends, sums, chunk, max_chunks, \
         single_tokens && N == n_seqs, stream))
     if (S <= 4) ZAI_SCAN(4, 1);

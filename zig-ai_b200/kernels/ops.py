@@ -36,13 +36,16 @@ _SIGNATURES = {
                    "zai_activation": [_P, _P, _I, _I, ctypes.c_longlong, _P],
                    "zai_weighted_sum": [_P, _P, _P, _I, _F, _F, ctypes.c_longlong, _P]},
     "causal_conv": {"zai_causal_conv": [_P, _I, _P, _I, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P]},
-    "selective_scan": {"zai_selective_scan": [_P, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I,
+    "selective_scan": {"zai_selective_scan": [_P, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I,
                                               _I, _P, _P, _P, _I, _I, _I, _P]},
     "min_gru": {"zai_min_gru": [_P, _P, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _I, _I, _P]},
     "gated_delta": {
         "zai_delta_prepare": [_P, _P, _P, _I, _P, _P, _I, _I, _P, _P, _I, _I, _I, _I, _F, _P],
         "zai_gated_delta": [_P, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
         "zai_gated_rmsnorm": [_P, _P, _P, _P, _I, _I, _F, _I, _I, _I, _P],
+        "zai_gated_delta_single_supports": [_I, _I],
+        "zai_gated_delta_single": [_P, _P, _I, _P, _P, _I, _P, _I, _I, _P, _P, _P, _F, _F, _P, _P, _I, _I, _I, _I, _I, _I, _I,
+                                   _P, _P],
     },
     "shortconv": {"zai_short_conv": [_P, _P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P]},
     "rope_kv": {
@@ -958,6 +961,7 @@ def weighted_sum(a, b, wa, wb):
     return out
 
 
+DELTA_SINGLE_MAX_ROWS = 16      # single-token steps of at most this many requests run the delta rule as one kernel
 CHUNKED_SCAN_MIN_ROWS = 256     # steps with prompt portions of this many rows or more run the linear recurrences in chunks
 
 
@@ -1018,10 +1022,12 @@ def selective_scan(x, proj, z, w_dt, b_dt, a_log, d_skip, state, step, dt_rank, 
     chunk, max_chunks = _scan_chunks(step, N, -(-I // (128 if S <= 16 else 64)))
     ends = torch.empty((max_chunks, I, S), dtype=torch.float32, device=x.device) if chunk else None
     sums = torch.empty((max_chunks, I), dtype=torch.float32, device=x.device) if chunk else None
-    # the step sizes' products dt_in . w_dt^T for all rows as one matrix product with a 32-bit result
-    dt_raw = linear(proj[:, :R], w_dt, out_dtype=torch.float32)
+    # the step sizes' products dt_in . w_dt^T for all rows as one matrix product with a 32-bit result; a step of
+    # single tokens sums them inside its kernel (a launch less a layer, and the weights are read once either way)
+    single = bool(step.decode_only and N == step.n_seqs)
+    dt_raw = None if single else linear(proj[:, :R], w_dt, out_dtype=torch.float32)
     _check(_fn("selective_scan", "zai_selective_scan")(
-        _ptr(y), _ptr(x), pp, ps, zp, zs, _dt(x), _ptr(dt_raw), _ptr(b_dt), _ptr(a_log), _ptr(d_skip), _ptr(state),
+        _ptr(y), _ptr(x), pp, ps, zp, zs, _dt(x), _ptr(dt_raw), _ptr(w_dt), _ptr(b_dt), _ptr(a_log), _ptr(d_skip), _ptr(state),
         _ptr(step.cu_q), _ptr(step.slot_ids), N, step.n_seqs, I, S, R, int(bool(write_state)), state.shape[0],
         _status_ptr(x.device), _ptr(ends), _ptr(sums), chunk, max_chunks, int(bool(step.decode_only)), _stream()),
         "selective_scan", 3 if chunk else 1)
@@ -1063,11 +1069,21 @@ def gated_delta(qkv, b, a, gate, a_log, dt_bias, norm_w, eps, state, step, heads
     if bs != as_ or state.dtype != torch.float32 or tuple(state.shape[1:]) != (H, D, V):
         raise KernelError("gated_delta: operands do not fit together")
     dev = qkv.device
+    lib = "gated_delta"
+    if step.decode_only and N == step.n_seqs and N <= DELTA_SINGLE_MAX_ROWS and _fn(lib, "zai_gated_delta_single_supports")(D, V):
+        # every request brings one token: norms, gates, the state's update and read-out and the output norm in one kernel
+        # (few requests: the step is a chain of launches and two fewer count; with many the states' bytes count and the
+        # three kernels stream them as fast, measured within the spread between runs at 64 requests)
+        out = torch.empty((N, H * V), dtype=qkv.dtype, device=dev)
+        _check(_fn(lib, "zai_gated_delta_single")(
+            _ptr(out), qp, qs, bp, ap, bs, gp, gs, _dt(qkv), _ptr(a_log), _ptr(dt_bias), _ptr(norm_w), float(eps),
+            float(unit_eps), _ptr(state), _ptr(step.slot_ids), N, H, G, D, V, int(bool(write_state)), state.shape[0],
+            _status_ptr(dev), _stream()), "gated_delta_single")
+        return out
     qk = torch.empty((N, 2, G, D), dtype=torch.float32, device=dev)
     bg = torch.empty((N, 2, H), dtype=torch.float32, device=dev)
     o = torch.empty((N, H * V), dtype=torch.float32, device=dev)
     out = torch.empty((N, H * V), dtype=qkv.dtype, device=dev)
-    lib = "gated_delta"
     _check(_fn(lib, "zai_delta_prepare")(_ptr(qk), _ptr(bg), qp, qs, bp, ap, bs, _dt(qkv), _ptr(a_log), _ptr(dt_bias), N, H, G, D,
                                          float(unit_eps), _stream()), "delta_prepare")
     vp = qp + 2 * G * D * qkv.element_size()
