@@ -75,8 +75,10 @@ def add_rmsnorm(h, delta, w, eps, out_dtype, delta_gamma=None, delta_eps=0.0):
     return (h * torch.rsqrt(ms + eps) * _f(w)).to(out_dtype)
 
 
-def linear(x, w, out_dtype=None):
+def linear(x, w, out_dtype=None, bias=None):
     out_dtype = out_dtype or x.dtype
+    if bias is not None:
+        return (_f(x) @ _f(w).T + _f(bias)).to(out_dtype)
     if x.dtype == w.dtype and x.dtype != torch.float32 and x.device.type == "cuda":
         return (x @ w.T).to(out_dtype)
     return (_f(x) @ _f(w).T).to(out_dtype)
@@ -125,14 +127,17 @@ def _rms(x, w, eps):
     return y * w if w is not None else y
 
 
-def _rotate(x, positions, rotary_dim, theta):
+def _rotate(x, positions, rotary_dim, theta, table=None):
     if rotary_dim == 0:
         return x
     half = rotary_dim // 2
-    i = torch.arange(half, dtype=torch.float32, device=x.device)
-    freq = torch.exp(-(2.0 * i / rotary_dim) * torch.log(torch.tensor(float(theta))))
-    ang = positions.to(torch.float32)[:, None] * freq[None, :]
-    cos, sin = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+    if table is not None:
+        cos, sin = table[:, None, :, 0], table[:, None, :, 1]
+    else:
+        i = torch.arange(half, dtype=torch.float32, device=x.device)
+        freq = torch.exp(-(2.0 * i / rotary_dim) * torch.log(torch.tensor(float(theta))))
+        ang = positions.to(torch.float32)[:, None] * freq[None, :]
+        cos, sin = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
     a, b = x[..., :half], x[..., half:rotary_dim]
     out = x.clone()
     out[..., :half] = a * cos - b * sin
@@ -185,7 +190,7 @@ def kv_write(k, v, step, cache, kv_heads, head_dim):
     cache.pages[page, 1, :, off, :] = v.reshape(N, kv_heads, head_dim).to(cache.pages.dtype)
 
 
-def paged_attention(q, step, cache, heads, kv_heads, head_dim, scale, window=None):
+def paged_attention(q, step, cache, heads, kv_heads, head_dim, scale, window=None, chunk=None):
     N = q.shape[0]
     D, ps = head_dim, cache.page_size
     out = torch.empty((N, heads * D), dtype=q.dtype, device=q.device)
@@ -211,6 +216,8 @@ def paged_attention(q, step, cache, heads, kv_heads, head_dim, scale, window=Non
         mask = kpos > qpos
         if window is not None:
             mask = mask | (kpos <= qpos - window)
+        if chunk is not None:
+            mask = mask | (kpos < qpos - qpos % chunk)
         sc = sc.masked_fill(mask[None], float("-inf"))
         p = torch.softmax(sc, dim=-1)
         o = torch.einsum("hnk,hkd->hnd", p, v).permute(1, 0, 2).reshape(b - a, heads * D)
@@ -410,3 +417,126 @@ def value_norm_pad(qkv, heads, kv_heads, dim, vdim, eps, normed=True):
         v = v * torch.rsqrt((v * v).mean(-1, keepdim=True) + eps)
     pad = lambda t: torch.nn.functional.pad(t, (0, Dp - t.shape[-1]))
     return torch.cat([pad(q).reshape(N, -1), pad(k).reshape(N, -1), pad(v).reshape(N, -1)], dim=1).to(qkv.dtype)
+
+
+# ---- what the layer-norm, chunked-attention and latent-attention designs add (the kernels of csrc/layernorm.cu,
+# qkv_prepare.cu, latent_attention.cu, and the additions to activation.cu, rope_kv.cu and attention*.cu)
+def add_layernorm(h, delta, w, b, eps, out_dtype):
+    if delta is not None:
+        h += _f(delta)
+    mu = h.mean(dim=-1, keepdim=True)
+    d = h - mu
+    var = (d * d).mean(dim=-1, keepdim=True)
+    return (d * torch.rsqrt(var + eps) * _f(w) + _f(b)).to(out_dtype)
+
+
+def stretched_frequencies(rotary_dim, theta, scaling):
+    """(frequencies in 64-bit, factor on cos and sin) of a rotation, stretched if `scaling` = (factor, original, fast, slow)."""
+    import math
+    i = torch.arange(rotary_dim // 2, dtype=torch.float64)
+    f = torch.pow(torch.tensor(float(theta), dtype=torch.float64), -2.0 * i / rotary_dim)
+    if scaling is None:
+        return f, 1.0
+    factor, original, fast, slow = scaling
+    where = lambda turns: rotary_dim * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(theta))
+    lo, hi = max(math.floor(where(fast)), 0), min(math.ceil(where(slow)), rotary_dim - 1)
+    ramp = torch.clamp((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+    return f / factor * ramp + f * (1.0 - ramp), 0.1 * math.log(factor) + 1.0
+
+
+def rope_table(step, rotary_dim, theta, device, scaling=None):
+    key = ("rope", rotary_dim, float(theta), scaling)
+    t = step.scratch.get(key)
+    if t is None:
+        f, mag = stretched_frequencies(rotary_dim, theta, scaling)
+        ang = step.positions.to(torch.float64)[:, None] * f[None, :]
+        t = torch.stack([torch.cos(ang) * mag, torch.sin(ang) * mag], dim=-1).to(torch.float32)
+        step.scratch[key] = t
+    return t
+
+
+def qkv_prepare(y, q_w, k_w, eps, scope, table, rot, step, cache, heads, kv_heads, dim, vdim, cache_dim, write=True):
+    """From projection rows y = [q (H D) | k (G D) | v (G Dv) | ...]: RMS norm of q and k (scope 0 none, 1 per head,
+    2 over the whole projection), rotation of pairs (i, i + rot/2) from the table, k and v into the pages (heads
+    `cache_dim` wide, zeros behind their own values); returns q [N, H * cache_dim]."""
+    N = y.shape[0]
+    H, G, D, Dv, Dp = heads, kv_heads, dim, vdim, cache_dim
+    q, k, v = _f(y[:, :H * D]), _f(y[:, H * D:(H + G) * D]), y[:, (H + G) * D:(H + G) * D + G * Dv]
+    if scope == 2:
+        q, k = _rms(q, q_w, eps), _rms(k, k_w, eps)
+    q, k = q.reshape(N, H, D), k.reshape(N, G, D)
+    if scope == 1:
+        q, k = _rms(q, q_w, eps), _rms(k, k_w, eps)
+    q, k = _rotate(q, step.positions, rot, 1.0, table), _rotate(k, step.positions, rot, 1.0, table)
+    pad = lambda t, n: torch.cat([t, t.new_zeros(t.shape[:-1] + (n - t.shape[-1],))], dim=-1)
+    if write:
+        page, off = _page_rows(step, cache)
+        cache.pages[page, 0, :, off, :] = pad(k, Dp).to(cache.pages.dtype)
+        cache.pages[page, 1, :, off, :] = pad(_f(v).reshape(N, G, Dv), Dp).to(cache.pages.dtype)
+    return pad(q, Dp).to(y.dtype).reshape(N, H * Dp)
+
+
+def sigmoid_gate(o, gate, heads, head_dim, per_head):
+    """o [N, heads * head_dim] times sigmoid(gate): gate [N, heads] (one number per head) or [N, heads * head_dim]."""
+    N = o.shape[0]
+    g = torch.sigmoid(_f(gate))
+    if per_head:
+        return (_f(o).reshape(N, heads, head_dim) * g[:, :, None]).reshape(N, heads * head_dim).to(o.dtype)
+    return (_f(o) * g).to(o.dtype)
+
+
+def head_linear(x, w):
+    """x [N, H, K] (a strided view is fine) times w [H, O, K] per head -> [N, H, O]."""
+    return torch.einsum("nhk,hok->nho", _f(x), _f(w)).to(x.dtype).contiguous()
+
+
+def latent_prepare(q, dkv, norm_w, eps, table, step, cache, heads, dim, rot_dim, rank):
+    """The rotated parts of the queries q [N, H, dim + rot_dim] -> [N, H, rot_dim]; if `dkv` [N, rank + rot_dim] is
+    given, the normed latent and the rotated shared key part of every row go into the request's pages."""
+    q_rot = _rotate(_f(q[:, :, dim:]), step.positions, rot_dim, 1.0, table).to(q.dtype).contiguous()
+    if dkv is not None:
+        c = _rms(_f(dkv[:, :rank]), norm_w, eps)
+        r = _rotate(_f(dkv[:, None, rank:]), step.positions, rot_dim, 1.0, table)[:, 0]
+        page, off = _page_rows(step, cache)
+        cache.pages[page, off, :] = torch.cat([c, r], dim=-1).to(cache.pages.dtype)
+    return q_rot
+
+
+def latent_attention(q_lat, q_rot, step, cache, heads, rank, rot_dim, scale):
+    """Causal attention of every head against the cached rows [latent | rotated key part]: scores
+    (q_lat . latent + q_rot . key part) * scale, output sum_j p_j latent_j, [N, H, rank]."""
+    N = q_lat.shape[0]
+    ps = cache.page_size
+    out = torch.empty((N, heads, rank), dtype=q_lat.dtype, device=q_lat.device)
+    cu, ctx = step.cu_q.tolist(), step.ctx_lens.tolist()
+    for s in range(step.n_seqs):
+        a, b = cu[s], cu[s + 1]
+        total = ctx[s] + (b - a)
+        n_pages = -(-total // ps)
+        if n_pages > cache.block_table.shape[1]:
+            _raise(16)
+        ids = _checked(cache.block_table[s, :n_pages].long(), cache.pages.shape[0], 4)
+        ids = torch.cat([ids, ids.new_zeros(n_pages - ids.shape[0])])
+        rows = _f(cache.pages[ids]).reshape(n_pages * ps, rank + rot_dim)[:total]
+        sc = (torch.einsum("nhr,kr->hnk", _f(q_lat[a:b]), rows[:, :rank])
+              + torch.einsum("nhr,kr->hnk", _f(q_rot[a:b]), rows[:, rank:])) * scale
+        qpos = torch.arange(ctx[s], total, device=q_lat.device)[:, None]
+        kpos = torch.arange(total, device=q_lat.device)[None, :]
+        sc = sc.masked_fill((kpos > qpos)[None], float("-inf"))
+        out[a:b] = torch.einsum("hnk,kr->nhr", torch.softmax(sc, dim=-1), rows[:, :rank]).to(q_lat.dtype)
+    return out
+
+
+def clamped_glu(gu, ff_dim, limit, alpha):
+    g = torch.clamp(_f(gu[:, :ff_dim]), max=limit)
+    u = torch.clamp(_f(gu[:, ff_dim:]), min=-limit, max=limit)
+    return (g * torch.sigmoid(alpha * g) * (u + 1.0)).to(gu.dtype)
+
+
+def linear_clamped_glu(x, w_gate_up, ff_dim, limit, alpha):
+    return clamped_glu(linear(x, w_gate_up), ff_dim, limit, alpha)
+
+
+def scale_softcap(logits, scale, cap):
+    y = _f(logits) * scale
+    return y if cap is None else cap * torch.tanh(y / cap)

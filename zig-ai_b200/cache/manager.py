@@ -12,7 +12,8 @@ The reference gives every attention layer a block table of its own drawing from 
   plane.  State groups hold one fixed-size 32-bit state per request and member, addressed by the
   request's slot.
 * pages are taken just before the step that fills them, given back when the request ends, and,
-  in a window group, as soon as every position of the page has left the window.
+  in a window group, as soon as every position of the page has left the window (in a group whose
+  layers see back to the start of a chunk of positions: as soon as the page lies before the chunk).
 * page 0 of every paged group and slot 0 are never handed out: padding rows of a fixed-shape
   decode batch point at them.
 """
@@ -106,7 +107,8 @@ class CacheManager:
         self.slots = IdPool(self.max_requests, first=1, what="slot")
         # host mirror of every block table, one row per slot, ready to be gathered into a step's batch
         self._rows = {gi: np.zeros((self.max_requests + 1, 16), dtype=np.int32) for gi in self.paged_groups()}
-        self._has_window = any(g.paged and g.need.window is not None for g in self.groups)
+        self._has_window = any(g.paged and (g.need.window is not None or getattr(g.need, "chunk", None) is not None)
+                               for g in self.groups)
         self.requests: Dict[object, RequestCache] = {}
         self.pages_reused = 0
         self._ever_used = [set() for _ in self.groups]
@@ -130,6 +132,9 @@ class CacheManager:
     def _first_needed_page(self, grp: CacheGroup, cached: int) -> int:
         """Logical pages below this index hold no position that a query at position >= `cached`
         may still read."""
+        chunk = getattr(grp.need, "chunk", None)
+        if chunk is not None:
+            return (cached // chunk) * chunk // self.page_size      # queries at positions >= cached see from their chunk's start
         if grp.need.window is None:
             return 0
         first_pos = max(cached - grp.need.window + 1, 0)

@@ -13,6 +13,16 @@ tensors' names.  With Dv != D every head is kept at max(D, Dv) with zeros behind
 change neither a score nor a sum), so the same pages and kernels serve; the q/k norm still averages
 over D.
 
+Further options, for designs that have them: `bias` (q, k and v projections with biases, added in the product);
+`norm_scope="whole"` (one RMS norm over all rows of the q projection, and one over all of k, weights of that size,
+before the split into heads); `chunk` (a query sees back to the start of its chunk of that many positions,
+counted from position 0 of the request: j <= i and j // chunk == i // chunk); `gate="head"` (a fourth
+projection of one number per query head; a head's output is multiplied by its sigmoid before the output
+projection); a position part that pairs dimensions (2i, 2i+1) or stretches its frequencies.  With any of them
+the projections run as one product q|k|v|gate and one kernel norms, rotates and writes the pages
+(`ops.qkv_prepare`); an interleaved pairing is turned into the half-split one by reordering the rows of the q
+and k projections (with their biases and norm weights) at load.
+
 Reference: projections src/transformer/hybrid_attn.zig:285-354, per-head norm :371-382 (device
 :719,723), scale 1/sqrt(D) :571, causal mask :587, softmax :578-600, query head hq reads kv head
 hq // (Hq/Hkv) :553-569 and src/cuda/paged_attention.cu:142, output projection :622-640; tensor
@@ -33,7 +43,7 @@ class Attention(Mixer):
 
     def __init__(self, hidden: int, heads: int, kv_heads: int, head_dim: int, qk_norm: bool, eps: float,
                  position: PartSpec, window=None, scale=None, kv_proj: bool = True, value_dim=None,
-                 value_norm: bool = False, names=None):
+                 value_norm: bool = False, names=None, bias: bool = False, norm_scope: str = "head", chunk=None, gate=None):
         self.hidden, self.heads, self.kv_heads, self.head_dim = int(hidden), int(heads), int(kv_heads), int(head_dim)
         if self.heads % self.kv_heads:
             raise ValueError(f"{self.heads} query heads cannot share {self.kv_heads} key/value heads evenly")
@@ -48,7 +58,22 @@ class Attention(Mixer):
             raise ValueError("a value norm or a value head size of its own needs the layer's own k/v projections")
         self.cache_dim = max(self.head_dim, self.value_dim)      # the head size of the pages and the kernels
         self.names = {"q": "attn_q.weight", "k": "attn_k.weight", "v": "attn_v.weight", "o": "attn_output.weight",
-                      "q_norm": "attn_q_norm.weight", "k_norm": "attn_k_norm.weight", **(names or {})}
+                      "q_norm": "attn_q_norm.weight", "k_norm": "attn_k_norm.weight", "q_bias": "attn_q.bias",
+                      "k_bias": "attn_k.bias", "v_bias": "attn_v.bias", "g": "attn_gate.weight", **(names or {})}
+        self.bias, self.norm_scope, self.gate = bool(bias), str(norm_scope), gate
+        self.chunk = None if chunk is None else int(chunk)
+        if self.norm_scope not in ("head", "whole") or self.gate not in (None, "head"):
+            raise ValueError("norm_scope is 'head' or 'whole'; gate is None or 'head'")
+        if self.chunk is not None and (self.chunk < 1 or self.window is not None):
+            raise ValueError("a chunk holds at least one position, and chunks and a window exclude each other")
+        # the options that the one-product, one-preparation path serves
+        self.prepared = bool(self.bias or self.norm_scope == "whole" or self.gate or self.chunk is not None
+                             or getattr(self.position, "pairing", "half_split") != "half_split"
+                             or getattr(self.position, "scaling", None) is not None)
+        if self.prepared and (self.value_norm or not self.kv_proj):
+            raise ValueError("value_norm and a borrowed cache are not combined with bias, whole norm, chunk or gate")
+        if self.prepared:
+            self.kernel_libs = ("qkv_prepare",)
 
     def params(self):
         q_dim, kv_dim = self.heads * self.head_dim, self.kv_heads * self.head_dim
@@ -58,16 +83,71 @@ class Attention(Mixer):
         if self.kv_proj:
             p[nm["k"]] = ParamDecl((kv_dim, self.hidden))
             p[nm["v"]] = ParamDecl((self.kv_heads * self.value_dim, self.hidden))
+        whole = self.norm_scope == "whole"
         if self.qk_norm:
-            p[nm["q_norm"]] = ParamDecl((self.head_dim,), "vector", init="norm_weight")
+            p[nm["q_norm"]] = ParamDecl((q_dim if whole else self.head_dim,), "vector", init="norm_weight")
             if self.kv_proj:
-                p[nm["k_norm"]] = ParamDecl((self.head_dim,), "vector", init="norm_weight")
+                p[nm["k_norm"]] = ParamDecl((kv_dim if whole else self.head_dim,), "vector", init="norm_weight")
+        if self.bias:
+            p[nm["q_bias"]] = ParamDecl((q_dim,), "vector", init="conv")
+            p[nm["k_bias"]] = ParamDecl((kv_dim,), "vector", init="conv")
+            p[nm["v_bias"]] = ParamDecl((self.kv_heads * self.value_dim,), "vector", init="conv")
+        if self.gate:
+            p[nm["g"]] = ParamDecl((self.heads, self.hidden))
         return p
 
     def cache_need(self):
-        return PagedKVNeed(self.kv_heads, self.cache_dim, self.window)
+        return PagedKVNeed(self.kv_heads, self.cache_dim, self.window, self.chunk)
+
+    def _bind_prepared(self, tensors, dtype):
+        """One matrix q|k|v|gate (and one bias vector), the rows of q and k in the order in which the rotation pairs
+        (i, i + dims/2)."""
+        nm, H, G, D, Dv, Dp = self.names, self.heads, self.kv_heads, self.head_dim, self.value_dim, self.cache_dim
+        perm = self.position.to_half_split(D)
+        idx = None if perm is None else torch.tensor(perm, dtype=torch.long, device=tensors[nm["q"]].device)
+
+        def heads_reordered(t, n_heads):          # t: [n_heads * D, ...] (rows of a projection, a bias, a whole norm's weight)
+            if idx is None or t is None:
+                return t
+            return t.reshape((n_heads, D) + tuple(t.shape[1:])).index_select(1, idx).reshape(t.shape).contiguous()
+
+        q, k, v = heads_reordered(tensors[nm["q"]], H), heads_reordered(tensors[nm["k"]], G), tensors[nm["v"]]
+        mats = [q, k, v] + ([tensors[nm["g"]]] if self.gate else [])
+        self.w_qkv = torch.cat(mats, dim=0).contiguous()
+        self.b_qkv = None
+        if self.bias:
+            b = [heads_reordered(tensors[nm["q_bias"]], H), heads_reordered(tensors[nm["k_bias"]], G), tensors[nm["v_bias"]]]
+            if self.gate:
+                b.append(b[0].new_zeros(H))
+            self.b_qkv = torch.cat(b).to(self.w_qkv.dtype).contiguous()
+        self.q_norm, self.k_norm = tensors.get(nm["q_norm"]), tensors.get(nm["k_norm"])
+        if self.norm_scope == "whole":
+            self.q_norm, self.k_norm = heads_reordered(self.q_norm, H), heads_reordered(self.k_norm, G)
+        elif idx is not None and self.q_norm is not None:
+            self.q_norm, self.k_norm = self.q_norm[idx].contiguous(), self.k_norm[idx].contiguous()
+        self.norm_eps = self.eps
+        self.w_o = tensors[nm["o"]]
+        if Dp != Dv:
+            w = self.w_o.reshape(self.hidden, H, Dv)
+            self.w_o = torch.cat([w, w.new_zeros(self.hidden, H, Dp - Dv)], dim=2).reshape(self.hidden, -1).contiguous()
+        self.gate_at = H * D + G * D + G * Dv
+        self.dtype = dtype
+
+    def _forward_prepared(self, x, step, cache, write_cache):
+        ops, H, G, D, Dv, Dp = step.ops, self.heads, self.kv_heads, self.head_dim, self.value_dim, self.cache_dim
+        y = ops.linear(x, self.w_qkv, bias=self.b_qkv)
+        dims, table = self.position.table(step, y.device)
+        scope = 0 if not self.qk_norm else (2 if self.norm_scope == "whole" else 1)
+        q = ops.qkv_prepare(y, self.q_norm, self.k_norm, self.norm_eps, scope, table, dims, step, cache, H, G, D, Dv, Dp,
+                            write_cache)
+        o = ops.paged_attention(q, step, cache, H, G, Dp, self.scale, self.window, chunk=self.chunk)
+        if self.gate:
+            o = ops.sigmoid_gate(o, y[:, self.gate_at:self.gate_at + H], H, Dp, True)
+        return ops.linear(o, self.w_o)
 
     def bind(self, tensors, dtype):
+        if self.prepared:
+            return self._bind_prepared(tensors, dtype)
         nm = self.names
         mats = [tensors[nm["q"]]]
         if self.kv_proj:
@@ -91,6 +171,8 @@ class Attention(Mixer):
         self.dtype = dtype
 
     def forward(self, x, step, cache, write_cache=True):
+        if self.prepared:
+            return self._forward_prepared(x, step, cache, write_cache)
         ops = step.ops
         write = write_cache and self.kv_proj
         qkv = ops.linear(x, self.w_qkv)

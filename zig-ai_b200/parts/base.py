@@ -83,11 +83,13 @@ class ParamDecl:
 # manager asks for nothing else, so a cache of one latent vector per position is a need like any other.
 @dataclass(frozen=True)
 class PagedKVNeed:
-    """Keys and values of every position (window None) or of the last `window` positions; a page is
+    """Keys and values of every position (window None), of the last `window` positions, or of the positions from
+    the start of the current chunk of `chunk` positions on (chunks are counted from position 0); a page is
     [2, kv_heads, page_size, head_dim] in the model's dtype."""
     kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    chunk: Optional[int] = None
 
     def page_shape(self, page_size: int) -> Tuple[int, ...]:
         return (2, self.kv_heads, page_size, self.head_dim)

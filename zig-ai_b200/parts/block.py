@@ -15,12 +15,14 @@ from .base import Block, NormedTerm, register_part
 class PreNormResidual(Block):
     graph_safe = True      # forward launches kernels only; nothing is read back to the host
 
-    def __init__(self, mixer, feed_forward, mixer_norm, ff_norm):
+    def __init__(self, mixer, mixer_norm, feed_forward=None, ff_norm=None):
         super().__init__()
         self.mixer_norm = self.sub("mixer_norm", "norm", mixer_norm)
         self.mixer = self.sub("mixer", "mixer", mixer)
-        self.ff_norm = self.sub("ff_norm", "norm", ff_norm)
-        self.feed_forward = self.sub("feed_forward", "feed_forward", feed_forward)
+        self.feed_forward = None                   # a layer may have no feed-forward (and then no second norm)
+        if feed_forward is not None:
+            self.ff_norm = self.sub("ff_norm", "norm", ff_norm)
+            self.feed_forward = self.sub("feed_forward", "feed_forward", feed_forward)
 
     def params(self):
         return {}
@@ -28,6 +30,8 @@ class PreNormResidual(Block):
     def forward(self, h, pending, step, cache, write_cache=True):
         r = self.mixer_norm.forward(h, pending, step, lazy=self.mixer.accepts_lazy_input)
         m = self.mixer.forward(r, step, self.cache_for(self.mixer, cache), write_cache)
+        if self.feed_forward is None:
+            return h, m
         r2 = self.ff_norm.forward(h, m, step, lazy=self.feed_forward.accepts_lazy_input)
         f = self.feed_forward.forward(r2, step)
         return h, f

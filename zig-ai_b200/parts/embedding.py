@@ -36,8 +36,10 @@ class LinearHead(Head):
     accepts_lazy_input = True     # x goes straight into a product
     graph_safe = True
 
-    def __init__(self, weight: str, tied: bool, vocab: int, hidden: int):
+    def __init__(self, weight: str, tied: bool, vocab: int, hidden: int, scale: float = 1.0, softcap=None):
         self.weight_name, self.tied, self.vocab, self.hidden = weight, bool(tied), int(vocab), int(hidden)
+        self.scale = float(scale)                                   # logits = product * scale ...
+        self.softcap = None if not softcap else float(softcap)      # ... then cap * tanh(logits / cap), in 32-bit
         self.w = None
 
     def params(self):
@@ -51,7 +53,10 @@ class LinearHead(Head):
         self.w = embedding.table
 
     def forward(self, x, step):
-        return step.ops.linear(x, self.w, out_dtype=torch.float32)
+        logits = step.ops.linear(x, self.w, out_dtype=torch.float32)
+        if self.scale != 1.0 or self.softcap is not None:
+            logits = step.ops.scale_softcap(logits, self.scale, self.softcap)
+        return logits
 
 
 register_part("embedding", "embedding", TokenEmbedding)

@@ -60,5 +60,35 @@ class DenseMlp(FeedForward):
         return ops.linear(ops.linear_activation(x, self.w_up, self.activation), self.w_down)
 
 
+class ClampedGlu(FeedForward):
+    """A gated feed-forward with bounded branches, no biases:
+
+        g = min(gate(x), limit);  u = clamp(up(x), -limit, limit);  out = down( g * sigmoid(alpha * g) * (u + 1) )
+
+    The gate and up matrices are stacked into one [2F, hidden] matrix at load.  `names` gives the tensors' names."""
+    accepts_lazy_input = True
+    graph_safe = True
+
+    def __init__(self, hidden: int, ff_dim: int, limit: float, alpha: float = 1.702, names=None):
+        self.hidden, self.ff_dim, self.limit, self.alpha = int(hidden), int(ff_dim), float(limit), float(alpha)
+        self.names = {"gate": "ffn_gate.weight", "up": "ffn_up.weight", "down": "ffn_down.weight", **(names or {})}
+
+    def params(self):
+        nm = self.names
+        return {nm["gate"]: ParamDecl((self.ff_dim, self.hidden)), nm["up"]: ParamDecl((self.ff_dim, self.hidden)),
+                nm["down"]: ParamDecl((self.hidden, self.ff_dim))}
+
+    def bind(self, tensors, dtype):
+        nm = self.names
+        self.w_gate_up = torch.cat([tensors[nm["gate"]], tensors[nm["up"]]], dim=0).contiguous()
+        self.w_down = tensors[nm["down"]]
+        self.dtype = dtype
+
+    def forward(self, x, step):
+        ops = step.ops
+        return ops.linear(ops.linear_clamped_glu(x, self.w_gate_up, self.ff_dim, self.limit, self.alpha), self.w_down)
+
+
 register_part("feed_forward", "swiglu", SwiGlu)
+register_part("feed_forward", "clamped_glu", ClampedGlu)
 register_part("feed_forward", "dense", DenseMlp)

@@ -1,4 +1,4 @@
-"""RMSNorm, fused with the residual addition that precedes it.
+"""Norms, fused with the residual addition that precedes them: RMSNorm, and the layer norm with weight and bias.
 
 `out = x * rsqrt(mean(x^2) + eps) * gamma` (eps inside the root), all in 32-bit (src/transformer/norm.zig:6-33; device
 version src/cuda/layer_kernels.cu:17-43).  The reference adds residuals with separate kernels
@@ -39,4 +39,35 @@ class RmsNorm(Norm):
         return x.materialize(step.ops)
 
 
+class LayerNorm(Norm):
+    """`(x - mean) / sqrt(var + eps) * weight + bias` over the row, the variance being the mean of the squared
+    deviations; all in 32-bit.  The pending term is added into the 32-bit residual stream by the same kernel."""
+    graph_safe = True
+    kernel_libs = ("layernorm",)
+
+    def __init__(self, size: int, eps: float, weight: str, bias: str = None):
+        self.size, self.eps, self.weight_name = int(size), float(eps), weight
+        self.bias_name = bias if bias is not None else weight + ".bias"
+        self.weight = self.bias = None
+
+    def params(self):
+        return {self.weight_name: ParamDecl((self.size,), "vector", init="norm_weight"),
+                self.bias_name: ParamDecl((self.size,), "vector", init="conv")}
+
+    def bind(self, tensors, dtype):
+        self.weight, self.bias = tensors[self.weight_name], tensors[self.bias_name]
+        self.dtype = dtype
+
+    def forward(self, h, delta, step, lazy=False, rows=None):
+        res = h if isinstance(h, Residual) else Residual(h)
+        ops = step.ops
+        if isinstance(delta, NormedTerm):
+            raise TypeError("a layer norm takes a plain pending term")
+        if rows is not None:
+            picked = ops.gather_add(res.data, delta, rows)
+            return ops.add_layernorm(picked, None, self.weight, self.bias, self.eps, self.dtype)
+        return ops.add_layernorm(res.data, delta, self.weight, self.bias, self.eps, self.dtype)
+
+
 register_part("norm", "rmsnorm", RmsNorm)
+register_part("norm", "layernorm", LayerNorm)
