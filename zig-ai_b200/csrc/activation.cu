@@ -117,3 +117,74 @@ ZAI_API int zai_weighted_sum(void* out, const void* a, const void* b, int dtype,
     ZAI_DISPATCH(dtype, return launch_pdl(weighted_sum_kernel<T>, dim3(blocks), dim3(threads), 0, stream, (T*)out, (const T*)a,
                                           (const T*)b, wa, wb, (size_t)total));
 }
+
+// ---- a gated activation with bounded branches on the stacked gate|up product, in 32-bit:
+//   g = min(gu[t, f], limit);  u = clamp(gu[t, F + f], -limit, limit);  a[t, f] = g * sigmoid(alpha * g) * (u + 1)
+template <typename T>
+__global__ void clamped_glu_kernel(T* __restrict__ out, const T* __restrict__ gu, int F, size_t total, float limit, float alpha) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const size_t t = i / F, f = i % F;
+    const float g = fminf(to_float(gu[t * 2 * F + f]), limit);
+    const float u = fminf(fmaxf(to_float(gu[t * 2 * F + F + f]), -limit), limit);
+    out[i] = from_float<T>(g / (1.f + expf(-alpha * g)) * (u + 1.f));
+}
+
+// bfloat16 rows with F a multiple of 8: one thread per 8 outputs, 16-byte loads and stores
+__global__ void clamped_glu_bf16x8_kernel(bf16* __restrict__ out, const bf16* __restrict__ gu, int F8, size_t total8, float limit,
+                                          float alpha) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total8) return;
+    const size_t t = i / F8, f = (i % F8) * 8;
+    const size_t F = (size_t)F8 * 8;
+    const uint4 g4 = *reinterpret_cast<const uint4*>(gu + t * 2 * F + f);
+    const uint4 u4 = *reinterpret_cast<const uint4*>(gu + t * 2 * F + F + f);
+    const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&g4);
+    const __nv_bfloat162* up = reinterpret_cast<const __nv_bfloat162*>(&u4);
+    uint4 o4;
+    __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&o4);
+    auto one = [&](float g, float u) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        return __fdividef(g, 1.f + __expf(-alpha * g)) * (u + 1.f);
+    };
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float2 g = __bfloat1622float2(gp[j]), u = __bfloat1622float2(up[j]);
+        op[j] = __floats2bfloat162_rn(one(g.x, u.x), one(g.y, u.y));
+    }
+    *reinterpret_cast<uint4*>(out + t * F + f) = o4;
+}
+
+ZAI_API int zai_clamped_glu(void* out, const void* gu, int dtype, int N, int F, float limit, float alpha, cudaStream_t stream) {
+    const size_t total = (size_t)N * F;
+    if (total == 0) return ZAI_OK;
+    const int threads = 256;
+    if (dtype == ZAI_BF16 && (F & 7) == 0) {
+        const size_t total8 = total / 8;
+        return launch_pdl(clamped_glu_bf16x8_kernel, dim3((unsigned)((total8 + threads - 1) / threads)), dim3(threads), 0, stream,
+                          (bf16*)out, (const bf16*)gu, F / 8, total8, limit, alpha);
+    }
+    const unsigned blocks = (unsigned)((total + threads - 1) / threads);
+    ZAI_DISPATCH(dtype, return launch_pdl(clamped_glu_kernel<T>, dim3(blocks), dim3(threads), 0, stream, (T*)out, (const T*)gu, F, total,
+                                          limit, alpha));
+}
+
+// ---- logits in place (32-bit):  x <- x * scale, then, with cap > 0,  x <- cap * tanh(x / cap)
+__global__ void scale_softcap_kernel(float* __restrict__ x, size_t total, float scale, float cap) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const float v = x[i] * scale;
+    x[i] = cap > 0.f ? cap * tanhf(v / cap) : v;
+}
+
+ZAI_API int zai_scale_softcap(float* x, long long total, float scale, float cap, cudaStream_t stream) {
+    if (total <= 0) return ZAI_OK;
+    return launch_pdl(scale_softcap_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, x, (size_t)total, scale, cap);
+}

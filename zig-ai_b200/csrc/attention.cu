@@ -1,7 +1,7 @@
 // Causal grouped-query attention over the paged cache, general kernel (any element type, head size,
 // page size, window): one warp per (row, query head).
 //
-//   s_j = q . k_j * scale  for cached positions j <= pos (and j > pos - window), same request
+//   s_j = q . k_j * scale  for cached positions j <= pos (and j > pos - window, or j in the chunk of pos), same request
 //   o   = sum_j softmax(s)_j v_j
 //
 // Scale 1/sqrt(D) by default (src/transformer/hybrid_attn.zig:571), causal bound on the token's
@@ -31,7 +31,7 @@ __global__ void paged_attention_warp_kernel(T* __restrict__ out, const T* __rest
     for (int d = lane; d < D; d += 32) qs[d] = to_float(qrow[d]) * scale;
     __syncwarp();
     const int kend = pos + 1;
-    const int kstart = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int kstart = zai_first_visible(pos, window);
     const size_t page_stride = (size_t)2 * Hkv * page_size * D;
     const size_t v_off = (size_t)Hkv * page_size * D;
     float m = -INFINITY, l = 0.f;

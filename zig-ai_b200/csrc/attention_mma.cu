@@ -159,8 +159,7 @@ __global__ void __launch_bounds__(PREFILL_WARPS * 32) prefill_mma_kernel(
     const size_t page_stride = (size_t)2 * Hkv * page_size * D;
     const size_t k_off = (size_t)hk * page_size * D, v_off = ((size_t)Hkv + hk) * page_size * D;
     const int kend = ctx + i0 + rows;                       // one past the last visible key of the block
-    int kbeg = 0;
-    if (window > 0) kbeg = max(ctx + i0 - window + 1, 0);
+    const int kbeg = zai_first_visible(ctx + i0, window);
     const int tile0 = kbeg / TILE, tile1 = (kend + TILE - 1) / TILE;
 
     // queries of the block: rows beyond the span are zeros
@@ -181,7 +180,7 @@ __global__ void __launch_bounds__(PREFILL_WARPS * 32) prefill_mma_kernel(
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;       // rows g and g+8 of the warp's 16
     const int g = lane >> 2, tq = lane & 3;
     const int p0 = ctx + i0 + warp * 16 + g, p1 = p0 + 8;          // positions of the two rows
-    const int lo0 = window > 0 ? p0 - window + 1 : 0, lo1 = window > 0 ? p1 - window + 1 : 0;
+    const int lo0 = zai_first_visible(p0, window), lo1 = zai_first_visible(p1, window);
     const bool warp_has_rows = warp * 16 < rows;
 
     for (int t = tile0; t < tile1; ++t) {
@@ -207,7 +206,7 @@ __global__ void __launch_bounds__(PREFILL_WARPS * 32) prefill_mma_kernel(
         const bf16* vt = sv + buf * TILE * ST;
         // a warp whose rows all lie before this tile's first key, or that has no rows, skips the tile
         const int warp_last_pos = ctx + i0 + warp * 16 + 15;
-        const int warp_first_lo = window > 0 ? ctx + i0 + warp * 16 - window + 1 : 0;
+        const int warp_first_lo = zai_first_visible(ctx + i0 + warp * 16, window);
         if (warp_has_rows && t * TILE <= warp_last_pos && (t + 1) * TILE > warp_first_lo) {
             float sc[8][4];
 #pragma unroll
@@ -215,7 +214,7 @@ __global__ void __launch_bounds__(PREFILL_WARPS * 32) prefill_mma_kernel(
 #pragma unroll
             for (int kb = 0; kb < 4; ++kb) qk_16keys<D>(sc[2 * kb], sc[2 * kb + 1], qf, kt + kb * 16 * ST, lane);
             float mx0 = -INFINITY, mx1 = -INFINITY;
-            const bool diag = (t + 1) * TILE - 1 > ctx + i0 + warp * 16 || window > 0;   // some element may be masked
+            const bool diag = (t + 1) * TILE - 1 > ctx + i0 + warp * 16 || window != 0;   // some element may be masked
             if (diag) {
 #pragma unroll
                 for (int nt = 0; nt < 8; ++nt) {
@@ -309,7 +308,7 @@ __global__ void __launch_bounds__(NTHREADS) decode_mma_kernel(
     pdl_wait();
     const int pos = positions[b];
     const int kend = pos + 1;
-    const int kstart = window > 0 ? max(pos - window + 1, 0) : 0;
+    const int kstart = zai_first_visible(pos, window);
     const int lo = max(chunk * CHUNK, kstart), hi = min((chunk + 1) * CHUNK, kend);
     if (lo >= hi) {
         if (tid < G) {
@@ -528,7 +527,7 @@ __global__ void __launch_bounds__(NTHREADS) decode_fused_kernel(const FusedDecod
     pdl_trigger();
     pdl_wait();
     const int pos = a.positions[b];
-    const int kstart = a.window > 0 ? max(pos - a.window + 1, 0) : 0;
+    const int kstart = zai_first_visible(pos, a.window);
     const bool has_new = a.write_kv && chunk == pos / a.chunk_keys;        // this block owns the new key
     const int kend = a.write_kv ? pos : pos + 1;                    // keys read from the pages
     const int lo = max(chunk * a.chunk_keys, kstart), hi = min((chunk + 1) * a.chunk_keys, kend);

@@ -246,7 +246,7 @@ __global__ void __launch_bounds__(AT_THREADS) prefill_tc_kernel(const __grid_con
         const int q_len = a.cu_q[s + 1] - row0, ctx = a.ctx_lens[s];
         rows = min(AT_BM, q_len - i0);                              // valid query rows of this block
         const int kend = ctx + i0 + rows;                           // one past the last visible key of the block
-        const int kbeg = a.window > 0 ? max(ctx + i0 - a.window + 1, 0) : 0;
+        const int kbeg = zai_first_visible(ctx + i0, a.window);
         int tile0 = kbeg / AT_BN, tile1 = (kend + AT_BN - 1) / AT_BN;
         if (SHARED) {                                               // this block's share of the key tiles
             const int per = (tile1 - tile0 + a.splits - 1) / a.splits;
@@ -352,7 +352,7 @@ __global__ void __launch_bounds__(AT_THREADS) prefill_tc_kernel(const __grid_con
             const int row = qd * 32 + lane;
             const bool valid = row < rows;
             const int qpos = ctx + i0 + row;                    // the row's position: keys 0..qpos are visible
-            const int klo = a.window > 0 ? max(qpos - a.window + 1, 0) : 0;
+            const int klo = zai_first_visible(qpos, a.window);
             const uint32_t tS = tmem_base + ((uint32_t)(qd * 32) << 16), tO = tS + AT_COL_O, tP = tS + AT_COL_P;
             const float c = a.scale_log2;
             bool alive = true;

@@ -144,7 +144,7 @@ __global__ void __maxnreg__(128) decode_tma_kernel(const __grid_constant__ CUten
     // A block without keys waits as a whole: what it stores (its empty partial sum) may lie in memory
     // that a kernel further back in the chain still uses, and nothing is stored before the wait.
     const int pos = a.positions[b];
-    const int kstart = a.window > 0 ? max(pos - a.window + 1, 0) : 0;
+    const int kstart = zai_first_visible(pos, a.window);
     const bool has_new = a.write_kv && chunk == pos / a.chunk_keys;
     const int kend = a.write_kv ? pos : pos + 1;
     const int lo = max(chunk * a.chunk_keys, kstart), hi = min((chunk + 1) * a.chunk_keys, kend);

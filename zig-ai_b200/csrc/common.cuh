@@ -48,6 +48,15 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 
 static inline int launch_status() { return (int)cudaGetLastError(); }
 
+// The first position that a query at `pos` sees.  `window` > 0: the last `window` positions; `window` < 0: back to
+// the start of the query's chunk of -window positions, chunks being counted from position 0 of the request;
+// 0: everything.  The value never decreases with `pos`, so a tile of query rows starts at its first row's.
+__host__ __device__ __forceinline__ int zai_first_visible(int pos, int window) {
+    if (window > 0) return pos - window + 1 > 0 ? pos - window + 1 : 0;
+    if (window < 0) return pos < 0 ? 0 : pos - pos % (-window);
+    return 0;
+}
+
 // ---- the status word of a step: one device int that kernels OR bits into and the host reads with the
 // step's results.  A kernel never traps and never touches memory outside the tensors it was given: an
 // id outside its bound is replaced by id 0 (page 0 and slot 0 are never handed to a request, padding

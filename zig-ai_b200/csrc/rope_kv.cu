@@ -15,9 +15,9 @@
 // One block per token; each warp takes heads in turn.
 #include "common.cuh"
 
-// table[t][i] = (cos, sin) of positions[t] * inv_freq[i]
+// table[t][i] = magnitude * (cos, sin) of positions[t] * inv_freq[i]
 __global__ void rope_table_kernel(float2* __restrict__ table, const int* __restrict__ positions,
-                                  const double* __restrict__ inv_freq, int N, int half) {
+                                  const double* __restrict__ inv_freq, int N, int half, double magnitude) {
     pdl_trigger();
     pdl_wait();
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
@@ -25,7 +25,7 @@ __global__ void rope_table_kernel(float2* __restrict__ table, const int* __restr
     const int t = idx / half, i = idx % half;
     double s, c;
     sincos((double)positions[t] * inv_freq[i], &s, &c);
-    table[idx] = make_float2((float)c, (float)s);
+    table[idx] = make_float2((float)(c * magnitude), (float)(s * magnitude));
 }
 
 template <typename T>
@@ -360,7 +360,17 @@ ZAI_API int zai_rope_table(float2* table, const int* positions, const double* in
                            cudaStream_t stream) {
     if (N <= 0 || half <= 0) return ZAI_OK;
     const int total = N * half;
-    return launch_pdl(rope_table_kernel, dim3((total + 127) / 128), dim3(128), 0, stream, table, positions, inv_freq, N, half);
+    return launch_pdl(rope_table_kernel, dim3((total + 127) / 128), dim3(128), 0, stream, table, positions, inv_freq, N, half, 1.0);
+}
+
+// The same table with cosines and sines multiplied by `magnitude` (a rotation stretched for longer contexts
+// scales both; its frequencies come stretched in `inv_freq`).
+ZAI_API int zai_rope_table_scaled(float2* table, const int* positions, const double* inv_freq, int N, int half, double magnitude,
+                                  cudaStream_t stream) {
+    if (N <= 0 || half <= 0) return ZAI_OK;
+    const int total = N * half;
+    return launch_pdl(rope_table_kernel, dim3((total + 127) / 128), dim3(128), 0, stream, table, positions, inv_freq, N, half,
+                      magnitude);
 }
 
 ZAI_API int zai_qk_norm_rope(const void* qkv, int qkv_cols, int dtype, const float* q_gamma, const float* k_gamma,

@@ -9,6 +9,7 @@ cuBLAS through `torch.matmul`, as the reference sends every projection to `cubla
 from __future__ import annotations
 
 import ctypes
+import math
 import os
 import sys
 import weakref
@@ -32,7 +33,16 @@ _SIGNATURES = {
     },
     "norm": {"zai_add_rmsnorm": [_P, _P, _P, _P, _I, _F, _I, _I, _P],
              "zai_add_normed_rmsnorm": [_P, _P, _P, _F, _P, _P, _I, _F, _I, _I, _P]},
+    "layernorm": {"zai_add_layernorm": [_P, _P, _P, _P, _P, _I, _F, _I, _I, _P]},
+    "qkv_prepare": {
+        "zai_qkv_prepare": [_P, _I, _I, _P, _P, _F, _I, _P, _I, _P, _P, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+        "zai_latent_prepare": [_P, _I, _P, _I, _I, _P, _F, _P, _P, _P, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P, _P],
+        "zai_sigmoid_gate": [_P, _P, ctypes.c_longlong, ctypes.c_longlong, _P, _I, _I, _I, _I, _I, _I, _P],
+    },
+    "latent_attention": {"zai_latent_attention": [_P, _P, _P, _P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P]},
     "activation": {"zai_silu_mul": [_P, _P, _I, _I, _I, _P],
+                   "zai_clamped_glu": [_P, _P, _I, _I, _I, _F, _F, _P],
+                   "zai_scale_softcap": [_P, ctypes.c_longlong, _F, _F, _P],
                    "zai_activation": [_P, _P, _I, _I, ctypes.c_longlong, _P],
                    "zai_weighted_sum": [_P, _P, _P, _I, _F, _F, ctypes.c_longlong, _P]},
     "causal_conv": {"zai_causal_conv": [_P, _I, _P, _I, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P]},
@@ -50,6 +60,7 @@ _SIGNATURES = {
     "shortconv": {"zai_short_conv": [_P, _P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P]},
     "rope_kv": {
         "zai_rope_table": [_P, _P, _P, _I, _I, _P],
+        "zai_rope_table_scaled": [_P, _P, _P, _I, _I, ctypes.c_double, _P],
         "zai_qk_norm_rope": [_P, _I, _I, _P, _P, _F, _P, _I, _P, _P, _P, _I, _P, _I, _P, _P,
                              _I, _I, _I, _I, _I, _I, _I, _P, _P],
         "zai_kv_write": [_P, _I, _P, _I, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _P, _P],
@@ -513,12 +524,17 @@ def _stream_product(x, w, epilogue, out_cols, out_dtype):
     return y
 
 
-def linear(x, w, out_dtype=None):
+def linear(x, w, out_dtype=None, bias=None):
     """x [N, K] times w [O, K] transposed.  x may be a LazyNorm.  Few rows in bfloat16 go to the
     fused few-rows kernel, many rows to the tcgen05 kernel where it is the faster one; a matrix kept
-    in 32-bit is multiplied in 32-bit; the rest is the library's."""
+    in 32-bit is multiplied in 32-bit; the rest is the library's.  With `bias` [O] (in w's dtype) the
+    library's product adds it before the result is rounded."""
     in_dtype = x.dtype
     out_dtype = out_dtype or in_dtype
+    if bias is not None:
+        if isinstance(x, LazyNorm):
+            x = x.materialize(sys.modules[__name__])
+        return _library_product(x, w, out_dtype, bias)
     if in_dtype == torch.bfloat16 and out_dtype in (torch.bfloat16, torch.float32):
         y = _skinny(x, w, _EPI_F32 if out_dtype == torch.float32 else _EPI_BF16, w.shape[0], out_dtype)
         if y is not None:
@@ -535,9 +551,15 @@ def linear(x, w, out_dtype=None):
     return _library_product(x, w, out_dtype)
 
 
-@_timed(lambda x, w, out_dtype: "head" if out_dtype == torch.float32 and x.dtype != torch.float32 else "products")
-def _library_product(x, w, out_dtype):
+@_timed(lambda x, w, out_dtype, bias=None: "head" if out_dtype == torch.float32 and x.dtype != torch.float32 else "products")
+def _library_product(x, w, out_dtype, bias=None):
     """The library's matrix product: true 32-bit where an operand or the result is 32-bit."""
+    if bias is not None:
+        if x.dtype == torch.float32 and torch.backends.cuda.matmul.allow_tf32:
+            torch.backends.cuda.matmul.allow_tf32 = False
+        if not (x.dtype == w.dtype == bias.dtype == out_dtype):
+            raise KernelError("a product with a bias takes operands, bias and result of one dtype")
+        return torch.addmm(bias, x, w.t())
     if x.dtype == torch.float32 or w.dtype == torch.float32 or out_dtype == torch.float32:
         if torch.backends.cuda.matmul.allow_tf32:
             torch.backends.cuda.matmul.allow_tf32 = False
@@ -683,28 +705,49 @@ def short_conv(bcx, conv_w, conv_b, state, step, taps, write_state=True):
 _inv_freq_cache = {}
 
 
-def inverse_frequencies(rotary_dim: int, theta: float, device) -> torch.Tensor:
-    """theta^(-2i/n) for i < n/2, computed in 64-bit."""
-    key = (rotary_dim, float(theta), str(device))
+def inverse_frequencies(rotary_dim: int, theta: float, device, scaling=None) -> torch.Tensor:
+    """theta^(-2i/n) for i < n/2, computed in 64-bit.  With `scaling` = (factor, original, fast, slow) the
+    frequencies are stretched for contexts longer than `original` positions: pair i keeps f_i where it turns more
+    than `fast` times within `original` positions, turns at f_i / factor where it turns fewer than `slow` times, and
+    in between the two are mixed by a ramp that is linear in i (see `rotation_magnitude` for what goes with it)."""
+    key = (rotary_dim, float(theta), str(device), scaling)
     t = _inv_freq_cache.get(key)
     if t is None:
         i = torch.arange(rotary_dim // 2, dtype=torch.float64)
-        t = torch.pow(torch.tensor(float(theta), dtype=torch.float64), -2.0 * i / rotary_dim).to(device)
+        t = torch.pow(torch.tensor(float(theta), dtype=torch.float64), -2.0 * i / rotary_dim)
+        if scaling is not None:
+            factor, original, fast, slow = (float(v) for v in scaling)
+            where = lambda turns: rotary_dim * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(float(theta)))
+            lo = max(math.floor(where(fast)), 0)
+            hi = min(math.ceil(where(slow)), rotary_dim - 1)
+            ramp = torch.clamp((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+            t = t / factor * ramp + t * (1.0 - ramp)
+        t = t.to(device)
         _inv_freq_cache[key] = t
     return t
 
 
+def rotation_magnitude(scaling) -> float:
+    """The factor on cosines and sines of a stretched rotation: 0.1 ln(factor) + 1."""
+    return 1.0 if scaling is None else 0.1 * math.log(float(scaling[0])) + 1.0
+
+
 @_timed("q/k norm, rotation, page write")
-def rope_table(step, rotary_dim: int, theta: float, device) -> torch.Tensor:
+def rope_table(step, rotary_dim: int, theta: float, device, scaling=None) -> torch.Tensor:
     """(cos, sin) of position * frequency for every row of the step, [N, rotary_dim/2, 2] 32-bit,
-    computed once per step and rotation and kept with the step."""
-    key = ("rope", rotary_dim, float(theta))
+    computed once per step and rotation and kept with the step.  `scaling`: see `inverse_frequencies`."""
+    key = ("rope", rotary_dim, float(theta), scaling)
     t = step.scratch.get(key)
     if t is None:
         half = rotary_dim // 2
         t = torch.empty((step.n_tokens, half, 2), dtype=torch.float32, device=device)
-        _check(_fn("rope_kv", "zai_rope_table")(_ptr(t), _ptr(step.positions), _ptr(inverse_frequencies(rotary_dim, theta, device)),
-                                                step.n_tokens, half, _stream()), "rope_table")
+        freq = inverse_frequencies(rotary_dim, theta, device, scaling)
+        if scaling is None:
+            _check(_fn("rope_kv", "zai_rope_table")(_ptr(t), _ptr(step.positions), _ptr(freq), step.n_tokens, half, _stream()),
+                   "rope_table")
+        else:
+            _check(_fn("rope_kv", "zai_rope_table_scaled")(_ptr(t), _ptr(step.positions), _ptr(freq), step.n_tokens, half,
+                                                           rotation_magnitude(scaling), _stream()), "rope_table")
         step.scratch[key] = t
     return t
 
@@ -757,12 +800,18 @@ def _attention_tickets(device, n):
     return t
 
 @_timed("attention")
-def paged_attention(q, step, cache, heads, kv_heads, head_dim, scale, window=None, impl=None):
+def paged_attention(q, step, cache, heads, kv_heads, head_dim, scale, window=None, impl=None, chunk=None):
     """Causal attention of the step's rows over their requests' pages.  bfloat16 runs on the
     tensor cores (a split-key kernel when every span is one token, else the flash-style kernel)
     for the head sizes those kernels have; everything else, and `impl="general"`, runs the
-    general kernel.  `impl="mma"` / `impl="tcgen05"` pick between the two span kernels."""
+    general kernel.  `impl="mma"` / `impl="tcgen05"` pick between the two span kernels.
+    `window`: a query sees the last `window` positions; `chunk`: it sees back to the start of its chunk of that
+    many positions (the kernels take the chunk as a negative window)."""
     _cuda(q)
+    if chunk is not None:
+        if window is not None:
+            raise KernelError("a window and chunks exclude each other")
+        window = -int(chunk)
     N = q.shape[0]
     if N != step.n_tokens:
         raise KernelError(f"{N} query rows for a step of {step.n_tokens} rows")
@@ -1114,3 +1163,133 @@ def value_norm_pad(qkv, heads, kv_heads, dim, vdim, eps, normed=True):
     _check(_fn("rope_kv", "zai_value_norm_pad")(_ptr(out), _ptr(qkv), qkv.shape[1], _dt(qkv), N, H, G, D, Dv, float(eps),
                                                 int(bool(normed)), _stream()), "value_norm_pad")
     return out
+
+
+# ----------------------------------------------------------------------------- layer norm, prepared projections, latent attention
+@_timed("norm")
+def add_layernorm(h, delta, w, b, eps, out_dtype):
+    """h += delta (in place, 32-bit), then the layer norm of h with weight w and bias b."""
+    _cuda(h, delta, w, b)
+    if h.dtype != torch.float32 or w.dtype != torch.float32 or b.dtype != torch.float32:
+        raise KernelError("the residual stream and norm weights are 32-bit")
+    N, H = h.shape
+    out = torch.empty((N, H), dtype=out_dtype, device=h.device)
+    if delta is not None and delta.dtype != out_dtype:
+        raise KernelError("the pending term should have the model's dtype")
+    _check(_fn("layernorm", "zai_add_layernorm")(_ptr(h), _ptr(delta), _ptr(w), _ptr(b), _ptr(out), _dt(out), float(eps), N, H,
+                                                 _stream()), "add_layernorm")
+    return out
+
+
+@_timed("q/k norm, rotation, page write")
+def qkv_prepare(y, q_w, k_w, eps, scope, table, rot, step, cache, heads, kv_heads, dim, vdim, cache_dim, write=True):
+    """From projection rows y = [q (H D) | k (G D) | v (G Dv) | ...]: the RMS norm of q and k (`scope` 0 none, 1 per head,
+    2 over the whole projection), the rotation of pairs (i, i + rot/2) from `table`, k and v into the pages (heads
+    `cache_dim` wide, zeros behind their own values); returns q [N, H * cache_dim]."""
+    _cuda(q_w, k_w, table)
+    yp, ys = _rows_view(y)
+    N = y.shape[0]
+    H, G, D, Dv, Dp = int(heads), int(kv_heads), int(dim), int(vdim), int(cache_dim)
+    if y.shape[1] < (H + G) * D + G * Dv:
+        raise KernelError("qkv_prepare: the rows do not hold q, k and v heads of these sizes")
+    pages, bt = cache.pages, cache.block_table
+    if pages.dtype != y.dtype or tuple(pages.shape[1:]) != (2, G, cache.page_size, Dp):
+        raise KernelError("the pages should have the activations' dtype and heads of the cache's size")
+    q = torch.empty((N, H * Dp), dtype=y.dtype, device=y.device)
+    _check(_fn("qkv_prepare", "zai_qkv_prepare")(
+        yp, ys, _dt(y), _ptr(q_w), _ptr(k_w), float(eps), int(scope), _ptr(table), int(rot), _ptr(step.positions), _ptr(step.seq_idx),
+        _ptr(bt), bt.shape[1], _ptr(pages), cache.page_size, _ptr(q), N, H, G, D, Dv, Dp, int(bool(write)), pages.shape[0],
+        _status_ptr(y.device), _stream()), "qkv_prepare")
+    return q
+
+
+@_timed("activation")
+def sigmoid_gate(o, gate, heads, head_dim, per_head):
+    """o [N, heads * head_dim] times sigmoid(gate): gate [N, heads] (one number per head) or [N, heads * head_dim]; a
+    column slice is fine for the gate."""
+    _cuda(o)
+    gp, gs = _rows_view(gate)
+    N = o.shape[0]
+    if gate.dtype != o.dtype or o.shape[1] != heads * head_dim or gate.shape[1] != (heads if per_head else heads * head_dim):
+        raise KernelError("sigmoid_gate: operands do not fit together")
+    out = torch.empty_like(o)
+    _check(_fn("qkv_prepare", "zai_sigmoid_gate")(_ptr(out), _ptr(o), heads * head_dim, head_dim, gp, gs, _dt(o), int(bool(per_head)),
+                                                  N, int(heads), int(head_dim), _stream()), "sigmoid_gate")
+    return out
+
+
+@_timed("products")
+def head_linear(x, w):
+    """x [N, H, K] (a strided view is fine) times w [H, O, K] per head -> [N, H, O]: the library's batched product,
+    true 32-bit where the operands are."""
+    if x.dtype == torch.float32 and torch.backends.cuda.matmul.allow_tf32:
+        torch.backends.cuda.matmul.allow_tf32 = False
+    N, H, _ = x.shape
+    out = torch.empty((N, H, w.shape[1]), dtype=x.dtype, device=x.device)
+    torch.bmm(x.transpose(0, 1), w.transpose(1, 2), out=out.transpose(0, 1))
+    return out
+
+
+@_timed("q/k norm, rotation, page write")
+def latent_prepare(q, dkv, norm_w, eps, table, step, cache, heads, dim, rot_dim, rank):
+    """The rotated parts of the queries q [N, H, dim + rot_dim] -> [N, H, rot_dim]; if `dkv` [N, rank + rot_dim] (a column
+    slice is fine) is given, the normed latent and the rotated shared key part of every row go into the request's pages."""
+    _cuda(norm_w, table)
+    N = q.shape[0]
+    H, D, Dr, R = int(heads), int(dim), int(rot_dim), int(rank)
+    if q.dim() != 3 or q.stride(2) != 1 or q.stride(1) != D + Dr or tuple(q.shape[1:]) != (H, D + Dr):
+        raise KernelError("latent_prepare: q is [N, heads, dim + rot_dim] with contiguous rows")
+    q_rot = torch.empty((N, H, Dr), dtype=q.dtype, device=q.device)
+    dp, ds = (None, 0) if dkv is None else _rows_view(dkv)
+    pages, bt = cache.pages, cache.block_table
+    if dkv is not None and (pages.dtype != q.dtype or tuple(pages.shape[1:]) != (cache.page_size, R + Dr)):
+        raise KernelError("the pages should have the activations' dtype and rows of rank + rot_dim values")
+    _check(_fn("qkv_prepare", "zai_latent_prepare")(
+        q.data_ptr(), q.stride(0), dp, ds, _dt(q), _ptr(norm_w), float(eps), _ptr(table), _ptr(step.positions), _ptr(step.seq_idx),
+        _ptr(bt), bt.shape[1], _ptr(pages), cache.page_size, _ptr(q_rot), N, H, D, Dr, R, pages.shape[0], _status_ptr(q.device),
+        _stream()), "latent_prepare")
+    return q_rot
+
+
+@_timed("attention")
+def latent_attention(q_lat, q_rot, step, cache, heads, rank, rot_dim, scale):
+    """Causal attention of every head against the cached rows [latent | rotated key part]: scores
+    (q_lat . latent + q_rot . key part) * scale, output sum_j p_j latent_j, [N, H, rank]."""
+    _cuda(q_lat, q_rot)
+    N = q_lat.shape[0]
+    H, R, Dr = int(heads), int(rank), int(rot_dim)
+    pages, bt = cache.pages, cache.block_table
+    if N != step.n_tokens or pages.dtype != q_lat.dtype or tuple(pages.shape[1:]) != (cache.page_size, R + Dr):
+        raise KernelError("latent_attention: operands do not fit together")
+    out = torch.empty((N, H, R), dtype=q_lat.dtype, device=q_lat.device)
+    _check(_fn("latent_attention", "zai_latent_attention")(
+        _ptr(out), _ptr(q_lat), _ptr(q_rot), _ptr(pages), _dt(q_lat), _ptr(bt), bt.shape[1], _ptr(step.positions), _ptr(step.seq_idx),
+        cache.page_size, N, H, R, Dr, float(scale), pages.shape[0], _status_ptr(q_lat.device), _stream()), "latent_attention")
+    return out
+
+
+@_timed("activation")
+def clamped_glu(gu, ff_dim, limit, alpha):
+    """min(g, limit) * sigmoid(alpha * min(g, limit)) * (clamp(u, -limit, limit) + 1) on the stacked gate|up rows."""
+    _cuda(gu)
+    N = gu.shape[0]
+    out = torch.empty((N, ff_dim), dtype=gu.dtype, device=gu.device)
+    _check(_fn("activation", "zai_clamped_glu")(_ptr(out), _ptr(gu), _dt(gu), N, int(ff_dim), float(limit), float(alpha), _stream()),
+           "clamped_glu")
+    return out
+
+
+def linear_clamped_glu(x, w_gate_up, ff_dim, limit, alpha):
+    """The stacked gate|up product (x may be a LazyNorm), then the bounded gated activation."""
+    return clamped_glu(linear(x, w_gate_up), ff_dim, limit, alpha)
+
+
+@_timed("head")
+def scale_softcap(logits, scale, cap):
+    """In place on 32-bit logits: times `scale`, then cap * tanh(logits / cap) if a cap is given."""
+    _cuda(logits)
+    if logits.dtype != torch.float32:
+        raise KernelError("logits are 32-bit")
+    _check(_fn("activation", "zai_scale_softcap")(_ptr(logits), logits.numel(), float(scale), float(cap or 0.0), _stream()),
+           "scale_softcap")
+    return logits
