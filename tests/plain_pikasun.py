@@ -116,8 +116,10 @@ def chunk_attention(h, w, p, m, eps):
         f = base_frequencies(rot["base"], rot["dims"])
         q = rotate_interleaved(q, pos, f, rot["dims"])
         k = rotate_interleaved(k, pos, f, rot["dims"])
-    size = m["mask"]["size"]
-    visible = (pos[None, :] <= pos[:, None]) & ((pos[None, :] // size) == (pos[:, None] // size))
+    visible = pos[None, :] <= pos[:, None]
+    if m.get("mask") is not None:                                # no mask given: plain causal attention
+        size = m["mask"]["size"]
+        visible = visible & ((pos[None, :] // size) == (pos[:, None] // size))
     gate = torch.sigmoid(h @ w[p + "g"].T)                       # [T, H]
     out = torch.zeros((T, H, Dv), dtype=F64)
     for hd in range(H):

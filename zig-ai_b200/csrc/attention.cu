@@ -84,15 +84,19 @@ ZAI_API int zai_paged_attention_general(void* out, const void* q, const void* pa
                                         int N, int Hq, int Hkv, int D, float scale, int window, int num_pages, int* status,
                                         cudaStream_t stream) {
     if (N <= 0) return ZAI_OK;
-    if (D < 1 || D > 256 || Hkv < 1 || Hq % Hkv != 0 || Hq > 65535) return ZAI_BAD_SIZE;
+    if (D < 1 || D > 512 || Hkv < 1 || Hq % Hkv != 0 || Hq > 65535) return ZAI_BAD_SIZE;
     const dim3 grid(N, Hq);
     const size_t smem = (size_t)D * sizeof(float);
     if (D <= 64) {
         ZAI_DISPATCH(dtype, return launch_pdl(paged_attention_warp_kernel<T, 2>, grid, dim3(32), smem, stream,
             (T*)out, (const T*)q, (const T*)pages, block_table, table_width, positions, seq_idx, page_size, Hq, Hkv,
             D, scale, window, num_pages, status));
-    } else {
+    } else if (D <= 256) {
         ZAI_DISPATCH(dtype, return launch_pdl(paged_attention_warp_kernel<T, 8>, grid, dim3(32), smem, stream,
+            (T*)out, (const T*)q, (const T*)pages, block_table, table_width, positions, seq_idx, page_size, Hq, Hkv,
+            D, scale, window, num_pages, status));
+    } else {
+        ZAI_DISPATCH(dtype, return launch_pdl(paged_attention_warp_kernel<T, 16>, grid, dim3(32), smem, stream,
             (T*)out, (const T*)q, (const T*)pages, block_table, table_width, positions, seq_idx, page_size, Hq, Hkv,
             D, scale, window, num_pages, status));
     }
