@@ -246,6 +246,8 @@ def run_ours(args):
         return run_mixed(args, cfg)
     if args.only == "vunolorn":
         return run_vunolorn(args)
+    if args.only == "pikasun":
+        return run_pikasun(args)
     if args.only == "long":
         return run_long(args)
     if args.only == "sample":
@@ -515,6 +517,160 @@ def run_vunolorn(args):
     print("|---|---|---|---|---|---|---|")
     for r in kernels:
         print(f"| {r['kernel']} | {r['point']} | {r['width']} | {r['us']} | {r['MB']} | {r['GB_per_s']} | {r['frac_of_copy_peak']} |")
+    return 0
+
+
+# ----------------------------------------------------------------------------- the Pikasun design beside LFM2
+def pikasun_config(width, layers=16, vocab=65536, ff=None):
+    """A Pikasun model of a real model's proportions: groups of four layers (attention inside chunks of 1024
+    positions with a quarter as many key/value heads as query heads; a latent layer of rank 256 with a rotated part
+    of 32; a latent layer that reads the one before; another latent layer of its own), head size 64 throughout, a
+    gated feed-forward behind every layer."""
+    heads = width // 64
+    ff = ff or 3 * width
+    mlp = {"kind": "dense", "ff": ff, "limit": 7.0}
+    stretched = {"base": 10000.0, "dims": 32, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}
+    latent = lambda src: {"type": "latent_attention", "mlp": dict(mlp),
+                          "mixer": dict({"heads": heads, "dim": 64, "rot_dim": 32, "vdim": 64, "kv_rank": 256, "scale": 96 ** -0.5,
+                                         "rot": dict(stretched)}, **({} if src is None else {"kv_from": src}))}
+    out = []
+    for i in range(layers):
+        if i % 4 == 0:
+            out.append({"type": "attention", "mlp": dict(mlp),
+                        "mixer": {"heads": heads, "kv_heads": max(heads // 4, 1), "dim": 64, "vdim": 64, "scale": 0.125,
+                                  "rot": {"base": 1000000.0, "dims": 64}, "mask": {"size": 1024}}})
+        else:
+            out.append(latent(i - 1 if i % 4 == 2 else None))
+    return {"architecture": "Pikasun", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "logit_scale": 1.0,
+            "logit_softcap": 30.0, "layers": out}
+
+
+def pikasun_kernel_rooflines(width, hbm_peak, flops_peak):
+    """The attention kernels of the design alone at the sizes of `pikasun_config(width)`, beside the like kernel of
+    LFM2 at the same width (grouped-query attention, head size 64): a portion of 2048 tokens and 64 single tokens over
+    contexts of 2048.  Latent attention against the tensor peak (its keys are read once per row and group of heads from
+    the L2 cache; the products decide) and, for single tokens, against the copy bandwidth (the cached rows decide)."""
+    import torch
+    from zig_ai_b200.cache.manager import CacheView
+    from zig_ai_b200.engine.batch import pack_step
+    from zig_ai_b200.kernels import ops
+    ops.require(torch.bfloat16, ("latent_attention", "qkv_prepare", "layernorm"))
+    dev, dt = torch.device("cuda"), torch.bfloat16
+    H, G, R, Dr, ps = width // 64, max(width // 256, 1), 256, 32, 64
+    g = torch.Generator().manual_seed(1)
+    rows = []
+
+    def step_of(ctx, q_lens):
+        spans, tables, at = [], [], 1
+        width_pages = max(-(-(c + n) // ps) for c, n in zip(ctx, q_lens))
+        for s_, (c, n) in enumerate(zip(ctx, q_lens)):
+            need = -(-(c + n) // ps)
+            tables.append(list(range(at, at + need)) + [0] * (width_pages - need))
+            at += need
+            spans.append((s_, c, [0] * n, [], s_ + 1))
+        return pack_step(ops, dt, dev, spans, {0: tables}), at
+
+    def timed(fn, reps=20):
+        for _ in range(3):
+            fn()
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        total = 0.0
+        for _ in range(reps):
+            flush.zero_()                                    # larger than L2: the timed call starts cold
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            total += a.elapsed_time(b)
+        return total / reps
+
+    for point, ctx, q_lens in (("2048-token portion", [0], [2048]), ("64 single tokens, context 2048", [2047] * 64, [1] * 64)):
+        step, n_pages = step_of(ctx, q_lens)
+        N = sum(q_lens)
+        keys = sum((c + n) * n - n * (n - 1) // 2 for c, n in zip(ctx, q_lens))           # (query, key) pairs
+        cached = sum(c + n for c, n in zip(ctx, q_lens))
+        lat_pages = (torch.randn(n_pages, ps, R + Dr, generator=g) * 0.3).to(dt).to(dev)
+        view = CacheView(0, lat_pages, step.block_tables[0], ps)
+        q_lat = torch.randn(N, H, R, generator=g).to(dt).to(dev)
+        q_rot = torch.randn(N, H, Dr, generator=g).to(dt).to(dev)
+        for label, impl in (("latent attention (tensor cores)", None), ("latent attention (general kernel)", "general")):
+            if impl == "general" and N > 64:
+                continue
+            ms = timed(lambda: ops.latent_attention(q_lat, q_rot, step, view, H, R, Dr, 0.1, impl=impl), 10)
+            rows.append((label, point, ms, 2.0 * keys * H * (2 * R + Dr), cached * (R + Dr) * 2 + N * H * (2 * R + Dr) * 2))
+        kv_pages = (torch.randn(n_pages, 2, G, ps, 64, generator=g) * 0.3).to(dt).to(dev)
+        kview = CacheView(0, kv_pages, step.block_tables[0], ps)
+        q = torch.randn(N, H * 64, generator=g).to(dt).to(dev)
+        for label, chunk in (("grouped-query attention (LFM2's kernel)", None), ("the same inside chunks of 1024", 1024)):
+            ms = timed(lambda: ops.paged_attention(q, step, kview, H, G, 64, 0.125, None, chunk=chunk), 10)
+            pairs = keys if chunk is None else sum(min(p % chunk + 1, p + 1) for c, n in zip(ctx, q_lens) for p in range(c, c + n))
+            rows.append((label, point, ms, 4.0 * pairs * H * 64, cached * 2 * G * 64 * 2 + 2 * N * H * 64 * 2))
+        h = torch.randn(N, width, generator=g).to(dev)
+        delta = torch.randn(N, width, generator=g).to(dt).to(dev)
+        w, b = torch.ones(width, device=dev), torch.zeros(width, device=dev)
+        rows.append(("layer norm + residual", point, timed(lambda: ops.add_layernorm(h, delta, w, b, 1e-6, dt)), 0.0, N * width * 12))
+        rows.append(("RMS norm + residual (LFM2's kernel)", point, timed(lambda: ops.add_rmsnorm(h, delta, w, 1e-6, dt)), 0.0, N * width * 12))
+    return [{"kernel": k, "point": p, "width": width, "us": round(ms * 1e3, 2), "GFLOP": round(fl / 1e9, 2), "MB": round(by / 1e6, 2),
+             "TFLOP_per_s": round(fl / ms / 1e9, 1), "of_tensor_peak": round(fl / ms / 1e9 / flops_peak, 4),
+             "GB_per_s": round(by / ms / 1e6, 1), "of_copy_peak": round(by / ms / 1e6 / hbm_peak, 4)} for k, p, ms, fl, by in rows]
+
+
+def run_pikasun(args):
+    """Prefill and decode throughput of the Pikasun design at two widths beside the LFM2 shape of the same width,
+    layer count and vocabulary; the time of a prefill and of a decode step by kernel class; and its attention and norm
+    kernels alone beside LFM2's.  JSON lines, then markdown tables."""
+    import torch
+    import zig_ai_b200 as z
+    from zig_ai_b200.config import config_from_dict
+    hbm_peak, flops_peak, peak_src = peaks()
+    rows, classes, kernels = [], [], []
+    for width, lfm2 in ((1024, "350m"), (2048, "1.2b")):
+        for label, cfg_dict in ((f"Pikasun-{width}", pikasun_config(width)), (f"LFM2-{lfm2.upper()}", shape_config(lfm2))):
+            cfg = config_from_dict(cfg_dict)
+            with tempfile.TemporaryDirectory(prefix="bench_pikasun_") as d:
+                z.write_random_model(cfg, 0, d)
+                eng = z.Engine(d, "bfloat16", max_num_seqs=64, max_batched_tokens=2048 + 64, max_model_len=CONTEXT,
+                               max_tokens=64 * CONTEXT, page_size=args.page_size)
+                nums = engine_numbers(eng)
+                prefill_ms = time_prefill(eng, reps=5)
+                T = PREFILL_TOKENS
+                rows.append({"model": label, "width": width, "matrix_params_M": round(nums["matrix_params"] / 1e6, 1),
+                             "point": "prefill 2048", "ms": round(prefill_ms, 3), "tokens_per_s": round(T / prefill_ms * 1e3),
+                             "matrix_TFLOP_per_s": round(2 * T * nums["matrix_params"] / prefill_ms / 1e9, 1)})
+                print(json.dumps(rows[-1]), flush=True)
+                for B in (1, 8, 64):
+                    dev_ms, e2e_ms, ctx_tokens, launches, _, _, _ = time_decode(eng, B, max(min(args.steps, 100), 20), args.warmup)
+                    step_bytes = 2 * nums["matrix_params"] + ctx_tokens * nums["kv_bytes_per_token"] + 2 * B * nums["state_bytes"]
+                    rows.append({"model": label, "width": width, "point": f"decode batch {B}", "ms": round(dev_ms, 4),
+                                 "e2e_ms": round(e2e_ms, 4), "tokens_per_s": round(B / dev_ms * 1e3),
+                                 "e2e_tokens_per_s": round(B / e2e_ms * 1e3), "GB_a_step": round(step_bytes / 1e9, 3),
+                                 "frac_of_copy_peak": round(step_bytes / (dev_ms * 1e-3) / 1e9 / hbm_peak, 3),
+                                 "launches_per_step": round(launches)})
+                    print(json.dumps(rows[-1]), flush=True)
+                g = random.Random(5)
+                V = eng.config.vocab_size
+                eng.flush()
+                pre = kernel_classes(eng, [("kc", [g.randrange(V) for _ in range(T)], [T - 1])])
+                dec = kernel_classes(eng, [(f"kc{i}", [g.randrange(V)], [0]) for i in range(64)])
+                classes.append({"model": label, "prefill_2048_ms_by_class": pre, "decode_64_first_token_ms_by_class": dec})
+                print(json.dumps(classes[-1]), flush=True)
+                del eng
+                torch.cuda.empty_cache()
+        kernels += pikasun_kernel_rooflines(width, hbm_peak, flops_peak)
+    for r in kernels:
+        print(json.dumps(r), flush=True)
+    print(f"\npeaks ({peak_src}): {hbm_peak:.0f} GB/s copy bandwidth, {flops_peak:.0f} TFLOP/s bf16 product (burst)\n")
+    print("| model | point | ms a step (device) | tokens/s (device) | tokens/s (end to end) | of the copy peak | launches a step |")
+    print("|---|---|---|---|---|---|---|")
+    for r in rows:
+        print(f"| {r['model']} | {r['point']} | {r['ms']} | {r['tokens_per_s']} | {r.get('e2e_tokens_per_s', '')} | "
+              f"{r.get('frac_of_copy_peak', '')} | {r.get('launches_per_step', '')} |")
+    print("\n| kernel | point | width | us | GFLOP | TFLOP/s | of the tensor peak | MB | GB/s | of the copy peak |")
+    print("|---|---|---|---|---|---|---|---|---|---|")
+    for r in kernels:
+        print(f"| {r['kernel']} | {r['point']} | {r['width']} | {r['us']} | {r['GFLOP']} | {r['TFLOP_per_s']} | {r['of_tensor_peak']} | "
+              f"{r['MB']} | {r['GB_per_s']} | {r['of_copy_peak']} |")
     return 0
 
 
@@ -871,9 +1027,9 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "gemm", "timeline", "table", "stream", "long", "sample", "vunolorn"],
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "gemm", "timeline", "table", "stream", "long", "sample", "vunolorn", "pikasun"],
                     help="profiling aid: run only the batch-8 decode steps or only the prefill (prints a short line); "
-                         "table: every figure of the 350M, 700M and 1.2B shapes (profiles/measurements.md); vunolorn: the "
+                         "table: every figure of the 350M, 700M and 1.2B shapes (profiles/measurements.md); pikasun: the Pikasun design beside LFM2 at equal width; vunolorn: the "
                          "Vunolorn hybrid at two widths beside LFM2 at equal width, and its recurrent kernels alone")
     ap.add_argument("--batch", type=int, default=8, help="with --only decode: the batch size; with --only stream: 24, 64 or "
                                                          "128 runs that row count only")

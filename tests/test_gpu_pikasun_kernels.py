@@ -198,9 +198,35 @@ def test_latent_attention_spans_and_single_tokens(dtype, H, R, Dr, ps):
         q_rot = torch.randn(N, H, Dr, generator=g).to(dtype).cuda()
         view = CacheView(0, pages, step.block_tables[0], ps)
         scale = (R + Dr) ** -0.5
-        a = o.latent_attention(q_lat, q_rot, step, view, H, R, Dr, scale)
         b = ref_ops.latent_attention(q_lat, q_rot, step, view, H, R, Dr, scale)
-        assert torch.allclose(a.float(), b.float(), **tol(dtype)), q_lens
+        for impl in (None, "general"):              # (bfloat16 with sizes the tensor-core kernel takes: that one, then the general one)
+            a = o.latent_attention(q_lat, q_rot, step, view, H, R, Dr, scale, impl=impl)
+            assert torch.allclose(a.float(), b.float(), **tol(dtype)), (q_lens, impl)
+        step.max_kv_len = 5000                      # more ranges of keys than any request needs (a captured graph's bound)
+        a2 = o.latent_attention(q_lat, q_rot, step, view, H, R, Dr, scale)
+        assert torch.allclose(a2.float(), b.float(), **tol(dtype)), q_lens
+    assert o.read_status() == 0
+
+
+@pytest.mark.parametrize("H,R,Dr,ps", [(16, 256, 32, 64), (20, 128, 64, 16), (128, 512, 64, 64), (4, 160, 16, 32)])
+def test_latent_attention_on_tensor_cores_many_rows(H, R, Dr, ps):
+    """Enough rows that no key ranges are made, spans of several hundred rows over long contexts, more than 16 heads,
+    ranks of one, two and four blocks of 128 columns and of a block and a quarter."""
+    o = ops()
+    dtype = torch.bfloat16
+    g = torch.Generator().manual_seed(21)
+    ctx, q_lens = [0, 700, 33], [400 if H < 100 else 40, 130 if H < 100 else 9, 1]
+    num_pages = sum(-(-(c + n) // ps) for c, n in zip(ctx, q_lens)) + 8
+    step = make_step(o, dtype, ctx, q_lens, ps, num_pages, 22)
+    pages = latent_pages(step, ctx, q_lens, ps, R + Dr, dtype, num_pages, g)
+    N = sum(q_lens)
+    q_lat = torch.randn(N, H, R, generator=g).to(dtype).cuda()
+    q_rot = torch.randn(N, H, Dr, generator=g).to(dtype).cuda()
+    view = CacheView(0, pages, step.block_tables[0], ps)
+    scale = (R + Dr) ** -0.5
+    a = o.latent_attention(q_lat, q_rot, step, view, H, R, Dr, scale, impl="mma")
+    b = ref_ops.latent_attention(q_lat, q_rot, step, view, H, R, Dr, scale)
+    assert torch.allclose(a.float(), b.float(), **tol(dtype))
     assert o.read_status() == 0
 
 

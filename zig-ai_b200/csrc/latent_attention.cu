@@ -10,7 +10,7 @@
 // (rows are padded by one word, so the lanes read different banks), the warp keeps an online softmax, and every lane
 // sums its share of the output dimensions.  Scores, weights and sums are 32-bit.  Keys are always visited from
 // position 0 in steps of 32, so a row's result does not depend on how the request was cut into steps or on its batch.
-#include "common.cuh"
+#include "mma_helpers.cuh"
 
 #define LA_WARPS 8
 #define LA_KEYS 32
@@ -107,6 +107,270 @@ static int launch_latent(void* out, const void* q_lat, const void* q_rot, const 
     return launch_pdl(latent_attention_kernel<T, MAXR>, dim3(N, (H + LA_WARPS - 1) / LA_WARPS), dim3(LA_WARPS * 32), smem, stream,
                       (T*)out, (const T*)q_lat, (const T*)q_rot, (const T*)pages, block_table, table_width, positions, seq_idx,
                       page_size, H, R, Dr, scale, num_pages, status);
+}
+
+// ------------------------------------------------------------------------------------------ tensor cores (bfloat16)
+// A warp owns one row of the step, 16 of its heads (the 16 rows of an m16n8k16 product), one block of up to 128
+// output columns and one range of `split_keys` keys.  Per tile of 32 cached rows, brought into the warp's own part
+// of shared memory by cp.async (two buffers): S = Q K^T over all R + Dr dimensions, the online softmax in 32-bit
+// (base 2), and O += P V with the tile's first R columns as V, P rounded to bfloat16 as the product's operand.
+// Warps never wait for one another.  With R > 128 every block of output columns computes S again (S is
+// (R + Dr) / 16 steps for 4 key groups, O 2 steps for 16 column groups: 1.5 times the work at R = 256, Dr = 32).
+// With several key ranges a warp leaves its unnormalised O, its maximum and its sum in scratch, and a second
+// kernel adds the ranges up in order; which range a key belongs to depends on its position alone.
+#define LM_KT 32           // keys per tile
+
+// A tile of LM_KT cached rows into shared memory: four lanes share a row (64 consecutive bytes an instruction); a lane
+// looks its four rows' pages up first, all at once, and then only issues copies.
+__device__ __forceinline__ void lm_load_tile(bf16* dst, int ST, const bf16* __restrict__ pages, const ZaiTableRow& table, int t0,
+                                             int khi, int page_size, int W, int lane) {
+    const int CH = W / 8;
+    const bf16* src[LM_KT / 8];
+#pragma unroll
+    for (int k = 0; k < LM_KT / 8; ++k) {
+        const int j = t0 + (lane >> 2) + 8 * k;
+        src[k] = j < khi ? pages + ((size_t)table.page(j / page_size) * page_size + j % page_size) * W : nullptr;
+    }
+    for (int c = lane & 3; c < CH; c += 4) {
+#pragma unroll
+        for (int k = 0; k < LM_KT / 8; ++k)
+            cp_async16(dst + ((lane >> 2) + 8 * k) * ST + c * 8, src[k] ? src[k] + c * 8 : pages, src[k] != nullptr);
+    }
+}
+
+template <int LM_COLS>       // output columns per warp: 128 or 256
+__global__ void __launch_bounds__(128) latent_attention_mma_kernel(
+    bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, const bf16* __restrict__ q_lat,
+    const bf16* __restrict__ q_rot, const bf16* __restrict__ pages, const int* __restrict__ block_table, int table_width,
+    const int* __restrict__ positions, const int* __restrict__ seq_idx, int page_size, int N, int H, int R, int Dr,
+    float scale_log2, int split_keys, int n_splits, int warps_per_block, int num_pages, int* __restrict__ status) {
+    extern __shared__ __align__(16) unsigned char lm_smem[];
+    const int W = R + Dr, ST = W + 8;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int HG = (H + 15) / 16, RCH = (R + LM_COLS - 1) / LM_COLS;
+    pdl_trigger();
+    pdl_wait();
+    long long w = (long long)blockIdx.x * warps_per_block + warp;
+    if (warp >= warps_per_block || w >= (long long)N * HG * RCH * n_splits) return;
+    const int split = (int)(w % n_splits);
+    w /= n_splits;
+    const int rc = (int)(w % RCH);
+    w /= RCH;
+    const int hg = (int)(w % HG);
+    const int t = (int)(w / HG);
+    bf16* sq = reinterpret_cast<bf16*>(lm_smem) + (size_t)warp * (16 + 2 * LM_KT) * ST;     // [16][ST] queries
+    bf16* sk = sq + 16 * ST;                                                                // 2 x [LM_KT][ST] cached rows
+    const int h0 = hg * 16, col0 = rc * LM_COLS;
+    const int g = lane >> 2, tq = lane & 3;
+    const int kend = positions[t] + 1;
+    const int kbeg = split * split_keys, khi = min(kend, kbeg + split_keys);
+    if (kbeg >= khi) {                                       // this range holds no key of the row
+        if (rc == 0 && tq == 0) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int h = h0 + g + 8 * e;
+                if (h < H) {
+                    float* ml = part_ml + (((size_t)t * H + h) * n_splits + split) * 2;
+                    ml[0] = -INFINITY;
+                    ml[1] = 0.f;
+                }
+            }
+        }
+        return;
+    }
+    const ZaiTableRow table{block_table + (size_t)seq_idx[t] * table_width, table_width, num_pages, status};
+    // the 16 heads' queries [latent part | rotated part]; heads beyond H are zeros
+    for (int idx = lane; idx < 16 * (W / 8); idx += 32) {
+        const int r = idx / (W / 8), c = (idx - r * (W / 8)) * 8;
+        const bool valid = h0 + r < H;
+        const size_t th = (size_t)t * H + (valid ? h0 + r : 0);
+        const bf16* src = c < R ? q_lat + th * R + c : q_rot + th * Dr + (c - R);
+        cp_async16(sq + r * ST + c, src, valid);
+    }
+    lm_load_tile(sk, ST, pages, table, kbeg, khi, page_size, W, lane);
+    cp_async_commit();
+    float o[LM_COLS / 8][4];
+#pragma unroll
+    for (int i = 0; i < LM_COLS / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;          // heads g and g+8 of the warp's 16
+    const int n_tiles = (khi - kbeg + LM_KT - 1) / LM_KT;
+    const int cols = min(LM_COLS, R - col0);                           // output columns of this warp (a multiple of 32)
+    const int a_row = (((lane >> 3) & 1) << 3) + (lane & 7), a_dof = (lane >> 4) << 3;
+    const int b_key = ((lane >> 4) << 3) + (lane & 7), b_dof = ((lane >> 3) & 1) << 3;
+    const int v_key = (((lane >> 3) & 1) << 3) + (lane & 7), v_dof = (lane >> 4) << 3;
+    for (int i = 0; i < n_tiles; ++i) {
+        const bf16* kt = sk + (size_t)(i & 1) * LM_KT * ST;
+        if (i + 1 < n_tiles) {
+            lm_load_tile(sk + (size_t)((i + 1) & 1) * LM_KT * ST, ST, pages, table, kbeg + (i + 1) * LM_KT, khi, page_size, W, lane);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncwarp();
+        float sc[4][4];
+#pragma unroll
+        for (int n = 0; n < 4; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
+        for (int ks = 0; ks < W / 16; ++ks) {
+            uint32_t a[4], b0[4], b1[4];
+            ldmatrix_x4(a, sq + a_row * ST + ks * 16 + a_dof);
+            ldmatrix_x4(b0, kt + b_key * ST + ks * 16 + b_dof);
+            ldmatrix_x4(b1, kt + (16 + b_key) * ST + ks * 16 + b_dof);
+            mma_bf16(sc[0], a, b0[0], b0[1]);
+            mma_bf16(sc[1], a, b0[2], b0[3]);
+            mma_bf16(sc[2], a, b1[0], b1[1]);
+            mma_bf16(sc[3], a, b1[2], b1[3]);
+        }
+        const int key0 = kbeg + i * LM_KT;
+        if (key0 + LM_KT > khi) {                            // the last tile: keys from khi on do not exist (or are not visible)
+#pragma unroll
+            for (int n = 0; n < 4; ++n)
+#pragma unroll
+                for (int e = 0; e < 2; ++e)
+                    if (key0 + n * 8 + 2 * tq + e >= khi) sc[n][e] = sc[n][2 + e] = -INFINITY;
+        }
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int n = 0; n < 4; ++n) {
+            mx0 = fmaxf(mx0, fmaxf(sc[n][0], sc[n][1]));
+            mx1 = fmaxf(mx1, fmaxf(sc[n][2], sc[n][3]));
+        }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);          // finite: every tile holds a visible key
+        const float u0 = n0 * scale_log2, u1 = n1 * scale_log2;
+        const float c0 = fast_exp2(m0 * scale_log2 - u0), c1 = fast_exp2(m1 * scale_log2 - u1);
+        m0 = n0;
+        m1 = n1;
+        l0 *= c0;
+        l1 *= c1;
+#pragma unroll
+        for (int j = 0; j < LM_COLS / 8; ++j) {
+            o[j][0] *= c0; o[j][1] *= c0; o[j][2] *= c1; o[j][3] *= c1;
+        }
+#pragma unroll
+        for (int n = 0; n < 4; ++n) {
+            sc[n][0] = fast_exp2(sc[n][0] * scale_log2 - u0);
+            sc[n][1] = fast_exp2(sc[n][1] * scale_log2 - u0);
+            sc[n][2] = fast_exp2(sc[n][2] * scale_log2 - u1);
+            sc[n][3] = fast_exp2(sc[n][3] * scale_log2 - u1);
+            l0 += sc[n][0] + sc[n][1];
+            l1 += sc[n][2] + sc[n][3];
+        }
+#pragma unroll
+        for (int kb = 0; kb < 2; ++kb) {
+            uint32_t pf[4];
+            pf[0] = pack_bf16(sc[2 * kb][0], sc[2 * kb][1]);
+            pf[1] = pack_bf16(sc[2 * kb][2], sc[2 * kb][3]);
+            pf[2] = pack_bf16(sc[2 * kb + 1][0], sc[2 * kb + 1][1]);
+            pf[3] = pack_bf16(sc[2 * kb + 1][2], sc[2 * kb + 1][3]);
+            const bf16* vrows = kt + (size_t)kb * 16 * ST + col0;
+#pragma unroll
+            for (int dp = 0; dp < LM_COLS / 16; ++dp) {
+                if (dp * 16 < cols) {
+                    uint32_t b[4];
+                    ldmatrix_x4_trans(b, vrows + v_key * ST + dp * 16 + v_dof);
+                    mma_bf16(o[2 * dp], pf, b[0], b[1]);
+                    mma_bf16(o[2 * dp + 1], pf, b[2], b[3]);
+                }
+            }
+        }
+        __syncwarp();                                        // the buffer is loaded again two tiles on
+    }
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    const int ha = h0 + g, hb = ha + 8;
+    if (n_splits == 1) {
+        const float inv0 = 1.f / l0, inv1 = 1.f / l1;
+#pragma unroll
+        for (int j = 0; j < LM_COLS / 8; ++j) {
+            const int d = j * 8 + 2 * tq;
+            if (d < cols) {
+                if (ha < H) *reinterpret_cast<uint32_t*>(out + ((size_t)t * H + ha) * R + col0 + d) = pack_bf16(o[j][0] * inv0, o[j][1] * inv0);
+                if (hb < H) *reinterpret_cast<uint32_t*>(out + ((size_t)t * H + hb) * R + col0 + d) = pack_bf16(o[j][2] * inv1, o[j][3] * inv1);
+            }
+        }
+        return;
+    }
+#pragma unroll
+    for (int j = 0; j < LM_COLS / 8; ++j) {
+        const int d = j * 8 + 2 * tq;
+        if (d < cols) {
+            if (ha < H) *reinterpret_cast<float2*>(part_o + (((size_t)t * H + ha) * n_splits + split) * R + col0 + d) = make_float2(o[j][0], o[j][1]);
+            if (hb < H) *reinterpret_cast<float2*>(part_o + (((size_t)t * H + hb) * n_splits + split) * R + col0 + d) = make_float2(o[j][2], o[j][3]);
+        }
+    }
+    if (rc == 0 && tq == 0) {
+        if (ha < H) {
+            float* ml = part_ml + (((size_t)t * H + ha) * n_splits + split) * 2;
+            ml[0] = m0 * scale_log2;
+            ml[1] = l0;
+        }
+        if (hb < H) {
+            float* ml = part_ml + (((size_t)t * H + hb) * n_splits + split) * 2;
+            ml[0] = m1 * scale_log2;
+            ml[1] = l1;
+        }
+    }
+}
+
+// out[t, h, :] = sum_c O_c 2^(m_c - m) / sum_c l_c 2^(m_c - m), the ranges taken in order
+__global__ void latent_combine_kernel(bf16* __restrict__ out, const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                      int R, int n_splits) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t th = blockIdx.x;
+    const float* ml = part_ml + th * n_splits * 2;
+    float m = -INFINITY;
+    for (int c = 0; c < n_splits; ++c) m = fmaxf(m, ml[2 * c]);
+    float l = 0.f;
+    for (int c = 0; c < n_splits; ++c) l += ml[2 * c + 1] * fast_exp2(ml[2 * c] - m);
+    const float inv = 1.f / l;
+    for (int d = threadIdx.x; d < R; d += blockDim.x) {
+        float acc = 0.f;
+        for (int c = 0; c < n_splits; ++c) {
+            const float wgt = fast_exp2(ml[2 * c] - m);              // an empty range: 2^-inf = 0, its O is never read
+            if (wgt > 0.f) acc += part_o[(th * n_splits + c) * R + d] * wgt;
+        }
+        out[th * R + d] = __float2bfloat16_rn(acc * inv);
+    }
+}
+
+ZAI_API int zai_latent_attention_mma_supports(int R, int Dr) {
+    const int W = R + Dr;
+    return R >= 32 && R % 32 == 0 && Dr >= 0 && W % 16 == 0 && (size_t)(16 + 2 * LM_KT) * (W + 8) * 2 <= 200 * 1024;
+}
+
+// bfloat16; part_o [N, H, n_splits, R] and part_ml [N, H, n_splits, 2] 32-bit scratch (unused with n_splits = 1).
+ZAI_API int zai_latent_attention_mma(void* out, float* part_o, float* part_ml, const void* q_lat, const void* q_rot, const void* pages,
+                                     const int* block_table, int table_width, const int* positions, const int* seq_idx,
+                                     int page_size, int N, int H, int R, int Dr, float scale, int split_keys, int n_splits,
+                                     int num_pages, int* status, cudaStream_t stream) {
+    if (N <= 0) return ZAI_OK;
+    if (!zai_latent_attention_mma_supports(R, Dr) || H < 1 || n_splits < 1 || split_keys < LM_KT || split_keys % LM_KT) return ZAI_BAD_SIZE;
+    const size_t per_warp = (size_t)(16 + 2 * LM_KT) * (R + Dr + 8) * 2;
+    int wpb = (int)((200 * 1024) / per_warp);
+    wpb = wpb > 4 ? 4 : wpb;
+    const int cols = R <= 128 ? 128 : 256;
+    const long long warps = (long long)N * ((H + 15) / 16) * ((R + cols - 1) / cols) * n_splits;
+    const long long blocks = (warps + wpb - 1) / wpb;
+    if (blocks > 0x7fffffffLL) return ZAI_BAD_SIZE;
+    static unsigned long long done = 0;
+    if (zai_first_on_device(&done)) {
+        cudaFuncSetAttribute(latent_attention_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaFuncSetAttribute(latent_attention_mma_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    }
+    auto kernel = cols == 128 ? latent_attention_mma_kernel<128> : latent_attention_mma_kernel<256>;
+    int rc = launch_pdl(kernel, dim3((unsigned)blocks), dim3(128), per_warp * wpb, stream, (bf16*)out, part_o,
+                        part_ml, (const bf16*)q_lat, (const bf16*)q_rot, (const bf16*)pages, block_table, table_width, positions,
+                        seq_idx, page_size, N, H, R, Dr, scale * 1.4426950408889634f, split_keys, n_splits, wpb, num_pages, status);
+    if (rc != 0 || n_splits == 1) return rc;
+    return launch_pdl(latent_combine_kernel, dim3((unsigned)((size_t)N * H)), dim3(128), 0, stream, (bf16*)out, (const float*)part_o,
+                      (const float*)part_ml, R, n_splits);
 }
 
 // out [N, H, R], q_lat [N, H, R], q_rot [N, H, Dr], pages [num_pages, page_size, R + Dr], all in `dtype`.

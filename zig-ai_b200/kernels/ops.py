@@ -39,7 +39,11 @@ _SIGNATURES = {
         "zai_latent_prepare": [_P, _I, _P, _I, _I, _P, _F, _P, _P, _P, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P, _P],
         "zai_sigmoid_gate": [_P, _P, ctypes.c_longlong, ctypes.c_longlong, _P, _I, _I, _I, _I, _I, _I, _P],
     },
-    "latent_attention": {"zai_latent_attention": [_P, _P, _P, _P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P]},
+    "latent_attention": {
+        "zai_latent_attention": [_P, _P, _P, _P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P],
+        "zai_latent_attention_mma_supports": [_I, _I],
+        "zai_latent_attention_mma": [_P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P, _P],
+    },
     "activation": {"zai_silu_mul": [_P, _P, _I, _I, _I, _P],
                    "zai_clamped_glu": [_P, _P, _I, _I, _I, _F, _F, _P],
                    "zai_scale_softcap": [_P, ctypes.c_longlong, _F, _F, _P],
@@ -1251,10 +1255,17 @@ def latent_prepare(q, dkv, norm_w, eps, table, step, cache, heads, dim, rot_dim,
     return q_rot
 
 
+LATENT_SPLIT_KEYS = 256          # keys per range where a step's rows are too few to fill the device
+LATENT_WARPS_WANTED = 1024       # from this many warps (rows x groups of 16 heads x blocks of output columns) on, no ranges
+USE_LATENT_MMA = os.environ.get("ZAI_LATENT_MMA", "1") == "1"
+
+
 @_timed("attention")
-def latent_attention(q_lat, q_rot, step, cache, heads, rank, rot_dim, scale):
+def latent_attention(q_lat, q_rot, step, cache, heads, rank, rot_dim, scale, impl=None):
     """Causal attention of every head against the cached rows [latent | rotated key part]: scores
-    (q_lat . latent + q_rot . key part) * scale, output sum_j p_j latent_j, [N, H, rank]."""
+    (q_lat . latent + q_rot . key part) * scale, output sum_j p_j latent_j, [N, H, rank].  bfloat16 with a rank
+    that is a multiple of 32 and rank + rot_dim a multiple of 16 runs on the tensor cores (a step of few rows split
+    into ranges of keys that a second kernel adds up); everything else, and `impl="general"`, runs the general kernel."""
     _cuda(q_lat, q_rot)
     N = q_lat.shape[0]
     H, R, Dr = int(heads), int(rank), int(rot_dim)
@@ -1262,6 +1273,20 @@ def latent_attention(q_lat, q_rot, step, cache, heads, rank, rot_dim, scale):
     if N != step.n_tokens or pages.dtype != q_lat.dtype or tuple(pages.shape[1:]) != (cache.page_size, R + Dr):
         raise KernelError("latent_attention: operands do not fit together")
     out = torch.empty((N, H, R), dtype=q_lat.dtype, device=q_lat.device)
+    if (impl != "general" and (USE_LATENT_MMA or impl == "mma") and q_lat.dtype == torch.bfloat16
+            and _fn("latent_attention", "zai_latent_attention_mma_supports")(R, Dr)):
+        warps = N * (-(-H // 16)) * (-(-R // (128 if R <= 128 else 256)))
+        n_splits = 1 if warps >= LATENT_WARPS_WANTED else max(-(-int(step.max_kv_len) // LATENT_SPLIT_KEYS), 1)
+        split_keys = LATENT_SPLIT_KEYS if n_splits > 1 else 1 << 30           # one range: all keys
+        part_o = part_ml = None
+        if n_splits > 1:
+            part_o = torch.empty((N, H, n_splits, R), dtype=torch.float32, device=q_lat.device)
+            part_ml = torch.empty((N, H, n_splits, 2), dtype=torch.float32, device=q_lat.device)
+        _check(_fn("latent_attention", "zai_latent_attention_mma")(
+            _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(q_lat), _ptr(q_rot), _ptr(pages), _ptr(bt), bt.shape[1],
+            _ptr(step.positions), _ptr(step.seq_idx), cache.page_size, N, H, R, Dr, float(scale), split_keys, n_splits,
+            pages.shape[0], _status_ptr(q_lat.device), _stream()), "latent_attention_mma", 2 if n_splits > 1 else 1)
+        return out
     _check(_fn("latent_attention", "zai_latent_attention")(
         _ptr(out), _ptr(q_lat), _ptr(q_rot), _ptr(pages), _dt(q_lat), _ptr(bt), bt.shape[1], _ptr(step.positions), _ptr(step.seq_idx),
         cache.page_size, N, H, R, Dr, float(scale), pages.shape[0], _status_ptr(q_lat.device), _stream()), "latent_attention")
