@@ -199,7 +199,8 @@ def test_latent_attention_spans_and_single_tokens(dtype, H, R, Dr, ps):
         view = CacheView(0, pages, step.block_tables[0], ps)
         scale = (R + Dr) ** -0.5
         b = ref_ops.latent_attention(q_lat, q_rot, step, view, H, R, Dr, scale)
-        for impl in (None, "general"):              # (bfloat16 with sizes the tensor-core kernel takes: that one, then the general one)
+        # (bfloat16 with sizes the tensor-core kernels take: the one the step's size picks, both by name, the general one)
+        for impl in (None, "general") + (("mma_rows", "mma_ranges") if dtype == torch.bfloat16 and R % 32 == 0 and Dr % 16 == 0 else ()):
             a = o.latent_attention(q_lat, q_rot, step, view, H, R, Dr, scale, impl=impl)
             assert torch.allclose(a.float(), b.float(), **tol(dtype)), (q_lens, impl)
         step.max_kv_len = 5000                      # more ranges of keys than any request needs (a captured graph's bound)
@@ -224,10 +225,24 @@ def test_latent_attention_on_tensor_cores_many_rows(H, R, Dr, ps):
     q_rot = torch.randn(N, H, Dr, generator=g).to(dtype).cuda()
     view = CacheView(0, pages, step.block_tables[0], ps)
     scale = (R + Dr) ** -0.5
-    a = o.latent_attention(q_lat, q_rot, step, view, H, R, Dr, scale, impl="mma")
     b = ref_ops.latent_attention(q_lat, q_rot, step, view, H, R, Dr, scale)
-    assert torch.allclose(a.float(), b.float(), **tol(dtype))
+    for impl in ("mma_rows", "mma_ranges"):
+        a = o.latent_attention(q_lat, q_rot, step, view, H, R, Dr, scale, impl=impl)
+        assert torch.allclose(a.float(), b.float(), **tol(dtype)), impl
     assert o.read_status() == 0
+
+
+@pytest.mark.parametrize("M", [1, 5, 8, 16, 40])
+@pytest.mark.parametrize("K,F,limit", [(256, 384, 1.0), (1024, 3072, 7.0), (192, 100, 0.5)])
+def test_product_with_the_bounded_gated_activation(M, K, F, limit):
+    """Few rows: the activation is the product kernel's epilogue; more rows: a kernel of its own behind the product."""
+    o = ops()
+    g = torch.Generator().manual_seed(23)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn(2 * F, K, generator=g) * K ** -0.5 * 2).to(torch.bfloat16).cuda()
+    a = o.linear_clamped_glu(x, w, F, limit, 1.702)
+    b = ref_ops.linear_clamped_glu(x, w, F, limit, 1.702)
+    assert a.shape == (M, F) and torch.allclose(a.float(), b.float(), atol=3e-2, rtol=3e-2)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

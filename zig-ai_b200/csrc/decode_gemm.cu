@@ -78,6 +78,9 @@ struct SkinnyArgs {
     int taps, state_rows, write_state;
     int l2_prefetch_bytes; // how much of its weight rows a block asks into L2 before it waits for the kernel before it
     NextWeights next;      // the weights of the product after this one: asked into L2 while this one runs
+    // gated epilogue with bounded branches (glu_limit > 0): g = min(gate, limit), u = clamp(up, -limit, limit),
+    // y = g * sigmoid(glu_slope * g) * (u + 1); glu_limit = 0: y = silu(gate) * up
+    float glu_limit, glu_slope;
 };
 
 __device__ __forceinline__ void cp_async16_zfill(void* smem, const void* gmem, bool valid) {
@@ -480,8 +483,15 @@ __global__ void __launch_bounds__(SG_WARPS * 32, 2) skinny_gemm_kernel(const Ski
                 if (tok >= a.M) continue;
                 const float lo = c[0][nt][e] * inv_tok[nt][e], hi = c[0][nt][2 + e] * inv_tok[nt][e];
                 if (EPI == EPI_SWIGLU) {
-                    if (row_lo >= 0)
-                        reinterpret_cast<bf16*>(a.y)[(size_t)tok * a.ldy + row_lo] = __float2bfloat16_rn(lo / (1.f + expf(-lo)) * hi);
+                    if (row_lo >= 0) {
+                        float gt = lo, up = hi, slope = 1.f;
+                        if (a.glu_limit > 0.f) {
+                            gt = fminf(lo, a.glu_limit);
+                            up = fminf(fmaxf(hi, -a.glu_limit), a.glu_limit) + 1.f;
+                            slope = a.glu_slope;
+                        }
+                        reinterpret_cast<bf16*>(a.y)[(size_t)tok * a.ldy + row_lo] = __float2bfloat16_rn(gt / (1.f + expf(-slope * gt)) * up);
+                    }
                 } else if (EPI == EPI_F32) {
                     if (row_lo >= 0) reinterpret_cast<float*>(a.y)[(size_t)tok * a.ldy + row_lo] = lo;
                     if (row_hi >= 0) reinterpret_cast<float*>(a.y)[(size_t)tok * a.ldy + row_hi] = hi;
@@ -845,9 +855,9 @@ static int skinny_run(SkinnyArgs& a, int epilogue, cudaStream_t stream) {
 // y = epilogue(x . W^T).  With `h` given, x = rmsnorm(h[row_idx] + delta[row_idx]) * gamma and, if
 // h_out is given, h_out = h + delta (32-bit).  epilogue: 0 bfloat16 [M, O]; 1 float [M, O];
 // 2 SwiGLU on W = gate|up stacked, y bfloat16 [M, O/2].
-ZAI_API int zai_skinny_gemm(void* y, const void* W, const void* x, const float* h, const void* delta,
-                            const float* gamma, const int* row_idx, float* h_out, float eps, int M, int O, int K,
-                            int epilogue, cudaStream_t stream) {
+static int skinny_gemm_run(void* y, const void* W, const void* x, const float* h, const void* delta,
+                           const float* gamma, const int* row_idx, float* h_out, float eps, int M, int O, int K,
+                           int epilogue, float glu_limit, float glu_slope, cudaStream_t stream) {
     if (epilogue == EPI_CONV || !zai_skinny_gemm_supports(M, O, K, epilogue, h != nullptr)) return ZAI_BAD_SIZE;
     const int cs = (!h && (epilogue == EPI_BF16 || epilogue == EPI_F32)) ? splitk_cluster(K) : 0;
     if (cs) {
@@ -864,6 +874,8 @@ ZAI_API int zai_skinny_gemm(void* y, const void* W, const void* x, const float* 
     a.W = (const bf16*)W; a.x = (const bf16*)x; a.h = h; a.delta = (const bf16*)delta; a.gamma = gamma;
     a.row_idx = row_idx; a.h_out = h_out; a.y = y; a.eps = eps; a.M = M; a.O = O; a.K = K;
     a.F = O / 2;
+    a.glu_limit = glu_limit;
+    a.glu_slope = glu_slope;
     a.ldy = epilogue == EPI_SWIGLU ? O / 2 : O;
     if (epilogue == EPI_SWIGLU) {
         skinny_plan(a.F * 2, false, K, &a.n_tiles, &a.half_tiles, &a.tpc, &a.sk, &a.units);   // 8 gate + 8 up rows per tile
@@ -871,6 +883,21 @@ ZAI_API int zai_skinny_gemm(void* y, const void* W, const void* x, const float* 
         skinny_plan(O, true, K, &a.n_tiles, &a.half_tiles, &a.tpc, &a.sk, &a.units);
     }
     return skinny_run(a, epilogue, stream);
+}
+
+ZAI_API int zai_skinny_gemm(void* y, const void* W, const void* x, const float* h, const void* delta,
+                            const float* gamma, const int* row_idx, float* h_out, float eps, int M, int O, int K,
+                            int epilogue, cudaStream_t stream) {
+    return skinny_gemm_run(y, W, x, h, delta, gamma, row_idx, h_out, eps, M, O, K, epilogue, 0.f, 1.f, stream);
+}
+
+// The gated epilogue with bounded branches on W = gate|up stacked, y bfloat16 [M, O/2]:
+// g = min(gate, limit), u = clamp(up, -limit, limit), y = g * sigmoid(slope * g) * (u + 1).
+ZAI_API int zai_skinny_gemm_clamped_glu(void* y, const void* W, const void* x, const float* h, const void* delta,
+                                        const float* gamma, const int* row_idx, float* h_out, float eps, int M, int O, int K,
+                                        float limit, float slope, cudaStream_t stream) {
+    if (!(limit > 0.f)) return ZAI_BAD_SIZE;
+    return skinny_gemm_run(y, W, x, h, delta, gamma, row_idx, h_out, eps, M, O, K, EPI_SWIGLU, limit, slope, stream);
 }
 
 // The short convolution's input projection with the convolution as its epilogue, for steps in which

@@ -138,6 +138,87 @@ __device__ __forceinline__ void lm_load_tile(bf16* dst, int ST, const bf16* __re
     }
 }
 
+// One tile of LM_KT cached rows at `kt` (its first key is `key0`; keys from `khi` on are not seen) against the warp's 16
+// query rows at `sq`: the scores, the online softmax (base 2) and O += P V for the warp's `cols` output columns from
+// column `col0` of the rows.  Every tile a warp is given holds at least one key it sees.
+template <int LM_COLS>
+__device__ __forceinline__ void lm_tile(float (&o)[LM_COLS / 8][4], float& m0, float& m1, float& l0, float& l1, const bf16* sq,
+                                        const bf16* kt, int ST, int W, int key0, int khi, int col0, int cols, float scale_log2,
+                                        int lane) {
+    const int tq = lane & 3;
+    const int a_row = (((lane >> 3) & 1) << 3) + (lane & 7), a_dof = (lane >> 4) << 3;
+    const int b_key = ((lane >> 4) << 3) + (lane & 7), b_dof = ((lane >> 3) & 1) << 3;
+    const int v_key = (((lane >> 3) & 1) << 3) + (lane & 7), v_dof = (lane >> 4) << 3;
+    float sc[4][4];
+#pragma unroll
+    for (int n = 0; n < 4; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
+    for (int ks = 0; ks < W / 16; ++ks) {
+        uint32_t a[4], b0[4], b1[4];
+        ldmatrix_x4(a, sq + a_row * ST + ks * 16 + a_dof);
+        ldmatrix_x4(b0, kt + b_key * ST + ks * 16 + b_dof);
+        ldmatrix_x4(b1, kt + (16 + b_key) * ST + ks * 16 + b_dof);
+        mma_bf16(sc[0], a, b0[0], b0[1]);
+        mma_bf16(sc[1], a, b0[2], b0[3]);
+        mma_bf16(sc[2], a, b1[0], b1[1]);
+        mma_bf16(sc[3], a, b1[2], b1[3]);
+    }
+    if (key0 + LM_KT > khi) {                                // the last tile: keys from khi on do not exist (or are not visible)
+#pragma unroll
+        for (int n = 0; n < 4; ++n)
+#pragma unroll
+            for (int e = 0; e < 2; ++e)
+                if (key0 + n * 8 + 2 * tq + e >= khi) sc[n][e] = sc[n][2 + e] = -INFINITY;
+    }
+    float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+    for (int n = 0; n < 4; ++n) {
+        mx0 = fmaxf(mx0, fmaxf(sc[n][0], sc[n][1]));
+        mx1 = fmaxf(mx1, fmaxf(sc[n][2], sc[n][3]));
+    }
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);          // finite: every tile holds a visible key
+    const float u0 = n0 * scale_log2, u1 = n1 * scale_log2;
+    const float c0 = fast_exp2(m0 * scale_log2 - u0), c1 = fast_exp2(m1 * scale_log2 - u1);
+    m0 = n0;
+    m1 = n1;
+    l0 *= c0;
+    l1 *= c1;
+#pragma unroll
+    for (int j = 0; j < LM_COLS / 8; ++j) {
+        o[j][0] *= c0; o[j][1] *= c0; o[j][2] *= c1; o[j][3] *= c1;
+    }
+#pragma unroll
+    for (int n = 0; n < 4; ++n) {
+        sc[n][0] = fast_exp2(sc[n][0] * scale_log2 - u0);
+        sc[n][1] = fast_exp2(sc[n][1] * scale_log2 - u0);
+        sc[n][2] = fast_exp2(sc[n][2] * scale_log2 - u1);
+        sc[n][3] = fast_exp2(sc[n][3] * scale_log2 - u1);
+        l0 += sc[n][0] + sc[n][1];
+        l1 += sc[n][2] + sc[n][3];
+    }
+#pragma unroll
+    for (int kb = 0; kb < 2; ++kb) {
+        uint32_t pf[4];
+        pf[0] = pack_bf16(sc[2 * kb][0], sc[2 * kb][1]);
+        pf[1] = pack_bf16(sc[2 * kb][2], sc[2 * kb][3]);
+        pf[2] = pack_bf16(sc[2 * kb + 1][0], sc[2 * kb + 1][1]);
+        pf[3] = pack_bf16(sc[2 * kb + 1][2], sc[2 * kb + 1][3]);
+        const bf16* vrows = kt + (size_t)kb * 16 * ST + col0;
+#pragma unroll
+        for (int dp = 0; dp < LM_COLS / 16; ++dp) {
+            if (dp * 16 < cols) {
+                uint32_t b[4];
+                ldmatrix_x4_trans(b, vrows + v_key * ST + dp * 16 + v_dof);
+                mma_bf16(o[2 * dp], pf, b[0], b[1]);
+                mma_bf16(o[2 * dp + 1], pf, b[2], b[3]);
+            }
+        }
+    }
+}
+
 template <int LM_COLS>       // output columns per warp: 128 or 256
 __global__ void __launch_bounds__(128) latent_attention_mma_kernel(
     bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, const bf16* __restrict__ q_lat,
@@ -195,9 +276,6 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;          // heads g and g+8 of the warp's 16
     const int n_tiles = (khi - kbeg + LM_KT - 1) / LM_KT;
     const int cols = min(LM_COLS, R - col0);                           // output columns of this warp (a multiple of 32)
-    const int a_row = (((lane >> 3) & 1) << 3) + (lane & 7), a_dof = (lane >> 4) << 3;
-    const int b_key = ((lane >> 4) << 3) + (lane & 7), b_dof = ((lane >> 3) & 1) << 3;
-    const int v_key = (((lane >> 3) & 1) << 3) + (lane & 7), v_dof = (lane >> 4) << 3;
     for (int i = 0; i < n_tiles; ++i) {
         const bf16* kt = sk + (size_t)(i & 1) * LM_KT * ST;
         if (i + 1 < n_tiles) {
@@ -208,75 +286,7 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(
             cp_async_wait<0>();
         }
         __syncwarp();
-        float sc[4][4];
-#pragma unroll
-        for (int n = 0; n < 4; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
-        for (int ks = 0; ks < W / 16; ++ks) {
-            uint32_t a[4], b0[4], b1[4];
-            ldmatrix_x4(a, sq + a_row * ST + ks * 16 + a_dof);
-            ldmatrix_x4(b0, kt + b_key * ST + ks * 16 + b_dof);
-            ldmatrix_x4(b1, kt + (16 + b_key) * ST + ks * 16 + b_dof);
-            mma_bf16(sc[0], a, b0[0], b0[1]);
-            mma_bf16(sc[1], a, b0[2], b0[3]);
-            mma_bf16(sc[2], a, b1[0], b1[1]);
-            mma_bf16(sc[3], a, b1[2], b1[3]);
-        }
-        const int key0 = kbeg + i * LM_KT;
-        if (key0 + LM_KT > khi) {                            // the last tile: keys from khi on do not exist (or are not visible)
-#pragma unroll
-            for (int n = 0; n < 4; ++n)
-#pragma unroll
-                for (int e = 0; e < 2; ++e)
-                    if (key0 + n * 8 + 2 * tq + e >= khi) sc[n][e] = sc[n][2 + e] = -INFINITY;
-        }
-        float mx0 = -INFINITY, mx1 = -INFINITY;
-#pragma unroll
-        for (int n = 0; n < 4; ++n) {
-            mx0 = fmaxf(mx0, fmaxf(sc[n][0], sc[n][1]));
-            mx1 = fmaxf(mx1, fmaxf(sc[n][2], sc[n][3]));
-        }
-        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
-        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
-        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
-        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-        const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);          // finite: every tile holds a visible key
-        const float u0 = n0 * scale_log2, u1 = n1 * scale_log2;
-        const float c0 = fast_exp2(m0 * scale_log2 - u0), c1 = fast_exp2(m1 * scale_log2 - u1);
-        m0 = n0;
-        m1 = n1;
-        l0 *= c0;
-        l1 *= c1;
-#pragma unroll
-        for (int j = 0; j < LM_COLS / 8; ++j) {
-            o[j][0] *= c0; o[j][1] *= c0; o[j][2] *= c1; o[j][3] *= c1;
-        }
-#pragma unroll
-        for (int n = 0; n < 4; ++n) {
-            sc[n][0] = fast_exp2(sc[n][0] * scale_log2 - u0);
-            sc[n][1] = fast_exp2(sc[n][1] * scale_log2 - u0);
-            sc[n][2] = fast_exp2(sc[n][2] * scale_log2 - u1);
-            sc[n][3] = fast_exp2(sc[n][3] * scale_log2 - u1);
-            l0 += sc[n][0] + sc[n][1];
-            l1 += sc[n][2] + sc[n][3];
-        }
-#pragma unroll
-        for (int kb = 0; kb < 2; ++kb) {
-            uint32_t pf[4];
-            pf[0] = pack_bf16(sc[2 * kb][0], sc[2 * kb][1]);
-            pf[1] = pack_bf16(sc[2 * kb][2], sc[2 * kb][3]);
-            pf[2] = pack_bf16(sc[2 * kb + 1][0], sc[2 * kb + 1][1]);
-            pf[3] = pack_bf16(sc[2 * kb + 1][2], sc[2 * kb + 1][3]);
-            const bf16* vrows = kt + (size_t)kb * 16 * ST + col0;
-#pragma unroll
-            for (int dp = 0; dp < LM_COLS / 16; ++dp) {
-                if (dp * 16 < cols) {
-                    uint32_t b[4];
-                    ldmatrix_x4_trans(b, vrows + v_key * ST + dp * 16 + v_dof);
-                    mma_bf16(o[2 * dp], pf, b[0], b[1]);
-                    mma_bf16(o[2 * dp + 1], pf, b[2], b[3]);
-                }
-            }
-        }
+        lm_tile<LM_COLS>(o, m0, m1, l0, l1, sq, kt, ST, W, kbeg + i * LM_KT, khi, col0, cols, scale_log2, lane);
         __syncwarp();                                        // the buffer is loaded again two tiles on
     }
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
@@ -318,6 +328,106 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(
     }
 }
 
+// Steps of many rows: the four warps of a block share the tiles of cached rows.  A warp still owns one row of the step,
+// 16 heads and a block of output columns; warps whose rows belong to one request form a group (in a long portion: all
+// four, consecutive rows or the same row's other heads and columns), the whole block copies the group's tiles into one
+// pair of buffers, and each member works on the tiles that hold keys it sees.  Groups of a block (at the border between two
+// requests, or single tokens of several requests) take their turns one after the other.
+template <int LM_COLS>
+__global__ void __launch_bounds__(128) latent_attention_rows_kernel(
+    bf16* __restrict__ out, const bf16* __restrict__ q_lat, const bf16* __restrict__ q_rot, const bf16* __restrict__ pages,
+    const int* __restrict__ block_table, int table_width, const int* __restrict__ positions, const int* __restrict__ seq_idx,
+    int page_size, int N, int H, int R, int Dr, float scale_log2, int num_pages, int* __restrict__ status) {
+    extern __shared__ __align__(16) unsigned char lm_smem[];
+    __shared__ int s_seq[4], s_kend[4];
+    const int W = R + Dr, ST = W + 8;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int HG = (H + 15) / 16, RCH = (R + LM_COLS - 1) / LM_COLS;
+    pdl_trigger();
+    pdl_wait();
+    long long w = (long long)blockIdx.x * 4 + warp;
+    const bool live = w < (long long)N * HG * RCH;
+    const int rc = live ? (int)(w % RCH) : 0;
+    w /= RCH;
+    const int hg = live ? (int)(w % HG) : 0;
+    const int t = live ? (int)(w / HG) : 0;
+    bf16* sq = reinterpret_cast<bf16*>(lm_smem) + (size_t)warp * 16 * ST;         // [16][ST] this warp's queries
+    bf16* sk = reinterpret_cast<bf16*>(lm_smem) + (size_t)4 * 16 * ST;            // 2 x [LM_KT][ST] the block's cached rows
+    const int h0 = hg * 16, col0 = rc * LM_COLS;
+    const int g = lane >> 2, tq = lane & 3;
+    const int my_seq = live ? seq_idx[t] : -1, my_kend = live ? positions[t] + 1 : 0;
+    if (lane == 0) {
+        s_seq[warp] = my_seq;
+        s_kend[warp] = my_kend;
+    }
+    if (live) {
+        for (int idx = lane; idx < 16 * (W / 8); idx += 32) {
+            const int r = idx / (W / 8), c = (idx - r * (W / 8)) * 8;
+            const bool valid = h0 + r < H;
+            const size_t th = (size_t)t * H + (valid ? h0 + r : 0);
+            const bf16* src = c < R ? q_lat + th * R + c : q_rot + th * Dr + (c - R);
+            cp_async16(sq + r * ST + c, src, valid);
+        }
+    }
+    cp_async_commit();
+    float o[LM_COLS / 8][4];
+#pragma unroll
+    for (int i = 0; i < LM_COLS / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+    const int cols = min(LM_COLS, R - col0);
+    __syncthreads();
+    for (int leader = 0; leader < 4; ++leader) {
+        const int seq = s_seq[leader];
+        bool first = seq >= 0;                               // (the same for every thread: all read shared memory)
+        for (int e = 0; e < leader; ++e) first = first && s_seq[e] != seq;
+        if (!first) continue;
+        int kmax = 0;
+        for (int e = leader; e < 4; ++e)
+            if (s_seq[e] == seq) kmax = max(kmax, s_kend[e]);
+        const bool member = my_seq == seq;
+        const ZaiTableRow table{block_table + (size_t)seq * table_width, table_width, num_pages, status};
+        const int n_tiles = (kmax + LM_KT - 1) / LM_KT;
+        // a tile: row tid / 4 of the 32, sixteen bytes a copy, four threads a row
+        auto load = [&](int i) {
+            const int j = i * LM_KT + (tid >> 2);
+            const bf16* src = j < kmax ? pages + ((size_t)table.page(j / page_size) * page_size + j % page_size) * W : nullptr;
+            bf16* dst = sk + (size_t)(i & 1) * LM_KT * ST + (tid >> 2) * ST;
+            for (int c = tid & 3; c < W / 8; c += 4) cp_async16(dst + c * 8, src ? src + c * 8 : pages, src != nullptr);
+        };
+        load(0);
+        cp_async_commit();
+        for (int i = 0; i < n_tiles; ++i) {
+            if (i + 1 < n_tiles) {
+                load(i + 1);
+                cp_async_commit();
+                cp_async_wait<1>();
+            } else {
+                cp_async_wait<0>();
+            }
+            __syncthreads();
+            if (member && i * LM_KT < my_kend)
+                lm_tile<LM_COLS>(o, m0, m1, l0, l1, sq, sk + (size_t)(i & 1) * LM_KT * ST, ST, W, i * LM_KT, my_kend, col0, cols,
+                                 scale_log2, lane);
+            __syncthreads();                                 // the buffer is loaded again two tiles on
+        }
+    }
+    if (!live) return;
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    const int ha = h0 + g, hb = ha + 8;
+    const float inv0 = 1.f / l0, inv1 = 1.f / l1;
+#pragma unroll
+    for (int j = 0; j < LM_COLS / 8; ++j) {
+        const int d = j * 8 + 2 * tq;
+        if (d < cols) {
+            if (ha < H) *reinterpret_cast<uint32_t*>(out + ((size_t)t * H + ha) * R + col0 + d) = pack_bf16(o[j][0] * inv0, o[j][1] * inv0);
+            if (hb < H) *reinterpret_cast<uint32_t*>(out + ((size_t)t * H + hb) * R + col0 + d) = pack_bf16(o[j][2] * inv1, o[j][3] * inv1);
+        }
+    }
+}
+
 // out[t, h, :] = sum_c O_c 2^(m_c - m) / sum_c l_c 2^(m_c - m), the ranges taken in order
 __global__ void latent_combine_kernel(bf16* __restrict__ out, const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                       int R, int n_splits) {
@@ -342,7 +452,7 @@ __global__ void latent_combine_kernel(bf16* __restrict__ out, const float* __res
 
 ZAI_API int zai_latent_attention_mma_supports(int R, int Dr) {
     const int W = R + Dr;
-    return R >= 32 && R % 32 == 0 && Dr >= 0 && W % 16 == 0 && (size_t)(16 + 2 * LM_KT) * (W + 8) * 2 <= 200 * 1024;
+    return R >= 32 && R % 32 == 0 && Dr >= 0 && W % 16 == 0 && (size_t)(4 * 16 + 2 * LM_KT) * (W + 8) * 2 <= 200 * 1024;
 }
 
 // bfloat16; part_o [N, H, n_splits, R] and part_ml [N, H, n_splits, 2] 32-bit scratch (unused with n_splits = 1).
@@ -352,10 +462,26 @@ ZAI_API int zai_latent_attention_mma(void* out, float* part_o, float* part_ml, c
                                      int num_pages, int* status, cudaStream_t stream) {
     if (N <= 0) return ZAI_OK;
     if (!zai_latent_attention_mma_supports(R, Dr) || H < 1 || n_splits < 1 || split_keys < LM_KT || split_keys % LM_KT) return ZAI_BAD_SIZE;
+    const int cols = R <= 128 ? 128 : 256;
+    if (n_splits == 1) {
+        // many rows: four warps a block share the tiles
+        const size_t smem = (size_t)(4 * 16 + 2 * LM_KT) * (R + Dr + 8) * 2;
+        const long long warps = (long long)N * ((H + 15) / 16) * ((R + cols - 1) / cols);
+        const long long blocks = (warps + 3) / 4;
+        if (blocks > 0x7fffffffLL || smem > 200 * 1024) return ZAI_BAD_SIZE;
+        static unsigned long long done_rows = 0;
+        if (zai_first_on_device(&done_rows)) {
+            cudaFuncSetAttribute(latent_attention_rows_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+            cudaFuncSetAttribute(latent_attention_rows_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        }
+        auto rows_kernel = cols == 128 ? latent_attention_rows_kernel<128> : latent_attention_rows_kernel<256>;
+        return launch_pdl(rows_kernel, dim3((unsigned)blocks), dim3(128), smem, stream, (bf16*)out, (const bf16*)q_lat,
+                          (const bf16*)q_rot, (const bf16*)pages, block_table, table_width, positions, seq_idx, page_size, N, H, R, Dr,
+                          scale * 1.4426950408889634f, num_pages, status);
+    }
     const size_t per_warp = (size_t)(16 + 2 * LM_KT) * (R + Dr + 8) * 2;
     int wpb = (int)((200 * 1024) / per_warp);
     wpb = wpb > 4 ? 4 : wpb;
-    const int cols = R <= 128 ? 128 : 256;
     const long long warps = (long long)N * ((H + 15) / 16) * ((R + cols - 1) / cols) * n_splits;
     const long long blocks = (warps + wpb - 1) / wpb;
     if (blocks > 0x7fffffffLL) return ZAI_BAD_SIZE;

@@ -85,6 +85,7 @@ _SIGNATURES = {
     "decode_gemm": {
         "zai_skinny_gemm_supports": [_I, _I, _I, _I, _I],
         "zai_skinny_gemm": [_P, _P, _P, _P, _P, _P, _P, _P, _F, _I, _I, _I, _I, _P],
+        "zai_skinny_gemm_clamped_glu": [_P, _P, _P, _P, _P, _P, _P, _P, _F, _I, _I, _I, _F, _F, _P],
         "zai_skinny_conv": [_P, _P, _P, _P, _P, _P, _P, _F, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
         "zai_skinny_hint_next": [_P, ctypes.c_longlong],
     },
@@ -408,8 +409,9 @@ def _hint_next_weights(w) -> None:
 
 
 @_timed(_product_class)
-def _skinny(x, w, epilogue, out_cols, out_dtype):
-    """The few-rows product kernel, if it takes these operands; else None."""
+def _skinny(x, w, epilogue, out_cols, out_dtype, glu=None):
+    """The few-rows product kernel, if it takes these operands; else None.  `glu` = (limit, slope): the gated epilogue
+    with bounded branches instead of SiLU(gate) * up."""
     lazy = isinstance(x, LazyNorm)
     M = (x.rows.numel() if x.rows is not None else x.residual.data.shape[0]) if lazy else x.shape[0]
     O, K = w.shape
@@ -421,19 +423,21 @@ def _skinny(x, w, epilogue, out_cols, out_dtype):
         return None
     y = torch.empty((M, out_cols), dtype=out_dtype, device=w.device)
     _hint_next_weights(w)
+    if glu is not None:
+        fn, tail = _fn("decode_gemm", "zai_skinny_gemm_clamped_glu"), (float(glu[0]), float(glu[1]), _stream())
+    else:
+        fn, tail = _fn("decode_gemm", "zai_skinny_gemm"), (epilogue, _stream())
     if lazy:
         res = x.residual
         _cuda(res.data, x.delta, x.gamma, x.rows)
         h_out = torch.empty_like(res.data) if (x.rows is None and x.delta is not None) else None
-        _check(_fn("decode_gemm", "zai_skinny_gemm")(
-            _ptr(y), _ptr(w), None, _ptr(res.data), _ptr(x.delta), _ptr(x.gamma), _ptr(x.rows), _ptr(h_out),
-            float(x.eps), M, O, K, epilogue, _stream()), "skinny_gemm")
+        _check(fn(_ptr(y), _ptr(w), None, _ptr(res.data), _ptr(x.delta), _ptr(x.gamma), _ptr(x.rows), _ptr(h_out),
+                  float(x.eps), M, O, K, *tail), "skinny_gemm")
         if h_out is not None:
             res.data = h_out
     else:
         _cuda(x)
-        _check(_fn("decode_gemm", "zai_skinny_gemm")(
-            _ptr(y), _ptr(w), _ptr(x), None, None, None, None, None, 0.0, M, O, K, epilogue, _stream()), "skinny_gemm")
+        _check(fn(_ptr(y), _ptr(w), _ptr(x), None, None, None, None, None, 0.0, M, O, K, *tail), "skinny_gemm")
     return y
 
 
@@ -1264,8 +1268,9 @@ USE_LATENT_MMA = os.environ.get("ZAI_LATENT_MMA", "1") == "1"
 def latent_attention(q_lat, q_rot, step, cache, heads, rank, rot_dim, scale, impl=None):
     """Causal attention of every head against the cached rows [latent | rotated key part]: scores
     (q_lat . latent + q_rot . key part) * scale, output sum_j p_j latent_j, [N, H, rank].  bfloat16 with a rank
-    that is a multiple of 32 and rank + rot_dim a multiple of 16 runs on the tensor cores (a step of few rows split
-    into ranges of keys that a second kernel adds up); everything else, and `impl="general"`, runs the general kernel."""
+    that is a multiple of 32 and rank + rot_dim a multiple of 16 runs on the tensor cores (steps of many rows: the four
+    warps of a block share the tiles of cached rows; steps of few rows: a warp a row and range of keys, the ranges added
+    up by a second kernel); everything else, and `impl="general"`, runs the general kernel."""
     _cuda(q_lat, q_rot)
     N = q_lat.shape[0]
     H, R, Dr = int(heads), int(rank), int(rot_dim)
@@ -1273,10 +1278,12 @@ def latent_attention(q_lat, q_rot, step, cache, heads, rank, rot_dim, scale, imp
     if N != step.n_tokens or pages.dtype != q_lat.dtype or tuple(pages.shape[1:]) != (cache.page_size, R + Dr):
         raise KernelError("latent_attention: operands do not fit together")
     out = torch.empty((N, H, R), dtype=q_lat.dtype, device=q_lat.device)
-    if (impl != "general" and (USE_LATENT_MMA or impl == "mma") and q_lat.dtype == torch.bfloat16
+    if (impl != "general" and (USE_LATENT_MMA or impl in ("mma", "mma_rows", "mma_ranges")) and q_lat.dtype == torch.bfloat16
             and _fn("latent_attention", "zai_latent_attention_mma_supports")(R, Dr)):
         warps = N * (-(-H // 16)) * (-(-R // (128 if R <= 128 else 256)))
         n_splits = 1 if warps >= LATENT_WARPS_WANTED else max(-(-int(step.max_kv_len) // LATENT_SPLIT_KEYS), 1)
+        if impl in ("mma_rows", "mma_ranges"):               # (tests pick the kernel whatever the step's size)
+            n_splits = 1 if impl == "mma_rows" else max(-(-int(step.max_kv_len) // LATENT_SPLIT_KEYS), 1)
         split_keys = LATENT_SPLIT_KEYS if n_splits > 1 else 1 << 30           # one range: all keys
         part_o = part_ml = None
         if n_splits > 1:
@@ -1305,7 +1312,12 @@ def clamped_glu(gu, ff_dim, limit, alpha):
 
 
 def linear_clamped_glu(x, w_gate_up, ff_dim, limit, alpha):
-    """The stacked gate|up product (x may be a LazyNorm), then the bounded gated activation."""
+    """The stacked gate|up product (x may be a LazyNorm) and the bounded gated activation: for few rows in bfloat16 the
+    activation is the product kernel's epilogue, else a kernel of its own behind the product."""
+    if x.dtype == torch.bfloat16:
+        y = _skinny(x, w_gate_up, _EPI_SWIGLU, ff_dim, torch.bfloat16, glu=(limit, alpha))
+        if y is not None:
+            return y
     return clamped_glu(linear(x, w_gate_up), ff_dim, limit, alpha)
 
 
