@@ -301,3 +301,37 @@ def test_products_with_a_bias_and_per_head(dtype):
         wh = (torch.randn(5, 24, 12, generator=g) * 0.3).to(dtype).cuda()
         a, b2 = o.head_linear(q, wh), ref_ops.head_linear(q, wh)
         assert a.shape == (N, 5, 24) and a.is_contiguous() and torch.allclose(a.float(), b2.float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("M", [1, 3, 8, 13, 16])
+@pytest.mark.parametrize("K,O", [(256, 512), (1024, 1536), (2048, 320), (192, 96)])
+def test_layer_norm_inside_the_few_rows_product(M, K, O):
+    """The layer norm (with the residual addition) as the product kernel's prologue against the norm's own kernel and
+    the product behind it: bfloat16 and 32-bit results, gathered rows, and the bounded gated activation as the epilogue;
+    the residual stream after the addition is the same either way."""
+    from zig_ai_b200.parts.base import LazyNorm, Residual
+    o = ops()
+    g = torch.Generator().manual_seed(31)
+    dt = torch.bfloat16
+    h = (torch.randn(M, K, generator=g) * 2 + 0.7).cuda()
+    delta = torch.randn(M, K, generator=g).to(dt).cuda()
+    gamma = (1 + 0.2 * torch.randn(K, generator=g)).cuda()
+    beta = (0.5 * torch.randn(K, generator=g)).cuda()
+    w = (torch.randn(O, K, generator=g) * K ** -0.5).to(dt).cuda()
+    h_ref = h.clone()
+    x_ref = ref_ops.add_layernorm(h_ref, delta, gamma, beta, 1e-5, dt)
+    for out_dtype in (dt, torch.float32):
+        res = Residual(h.clone())
+        got = o.linear(LazyNorm(res, delta, gamma, 1e-5, dt, beta=beta), w, out_dtype=out_dtype)
+        want = ref_ops.linear(x_ref, w, out_dtype)
+        assert torch.allclose(got.float(), want.float(), atol=3e-2, rtol=3e-2), out_dtype
+        assert torch.allclose(res.data, h_ref, atol=1e-6, rtol=0)
+    rows = torch.tensor([M - 1, 0], dtype=torch.int32).cuda()
+    res = Residual(h.clone())
+    got = o.linear(LazyNorm(res, delta, gamma, 1e-5, dt, rows=rows, beta=beta), w, out_dtype=torch.float32)
+    assert torch.allclose(got, ref_ops.linear(x_ref[rows.long()], w, torch.float32), atol=3e-2, rtol=3e-2)
+    if O % 2 == 0:
+        res = Residual(h.clone())
+        got = o.linear_clamped_glu(LazyNorm(res, delta, gamma, 1e-5, dt, beta=beta), w, O // 2, 0.8, 1.702)
+        want = ref_ops.linear_clamped_glu(x_ref, w, O // 2, 0.8, 1.702)
+        assert got.shape == (M, O // 2) and torch.allclose(got.float(), want.float(), atol=3e-2, rtol=3e-2)

@@ -81,6 +81,11 @@ struct SkinnyArgs {
     // gated epilogue with bounded branches (glu_limit > 0): g = min(gate, limit), u = clamp(up, -limit, limit),
     // y = g * sigmoid(glu_slope * g) * (u + 1); glu_limit = 0: y = silu(gate) * up
     float glu_limit, glu_slope;
+    // layer norm instead of RMS norm (norm variants only): the row's mean is taken off before the squares are summed,
+    // and beta_dot[o] = sum_k W[o, k] * beta[k] (the norm's bias through the product, made once per matrix) is added to
+    // the scaled sums
+    int center;
+    const float* beta_dot;
 };
 
 __device__ __forceinline__ void cp_async16_zfill(void* smem, const void* gmem, bool valid) {
@@ -297,6 +302,21 @@ __global__ void __launch_bounds__(SG_WARPS * 32, 2) skinny_gemm_kernel(const Ski
                 continue;
             }
             const size_t src = (size_t)(m < SG_WARPS ? src_row0 : src_row1) * K;
+            float mean = 0.f;
+            if (a.center) {                                  // a first walk over the row for its mean (the second one hits the cache)
+                float s4 = 0.f;
+                for (int k = lane * 4; k < K; k += 128) {
+                    const float4 v = *reinterpret_cast<const float4*>(a.h + src + k);
+                    s4 += (v.x + v.y) + (v.z + v.w);
+                    if (a.delta) {
+                        const uint2 d = *reinterpret_cast<const uint2*>(a.delta + src + k);
+                        const __nv_bfloat162 d0 = *reinterpret_cast<const __nv_bfloat162*>(&d.x);
+                        const __nv_bfloat162 d1 = *reinterpret_cast<const __nv_bfloat162*>(&d.y);
+                        s4 += (__low2float(d0) + __high2float(d0)) + (__low2float(d1) + __high2float(d1));
+                    }
+                }
+                mean = warp_sum(s4) / (float)K;
+            }
             float ss = 0.f;
             for (int kq = lane * 4; kq < K; kq += 1024) {
                 float4 v[8];
@@ -320,8 +340,9 @@ __global__ void __launch_bounds__(SG_WARPS * 32, 2) skinny_gemm_kernel(const Ski
                             const __nv_bfloat162 d1 = *reinterpret_cast<const __nv_bfloat162*>(&d[u].y);
                             w.x += __low2float(d0); w.y += __high2float(d0); w.z += __low2float(d1); w.w += __high2float(d1);
                         }
-                        ss += w.x * w.x + w.y * w.y + w.z * w.z + w.w * w.w;
                         if (a.h_out && blockIdx.x == 0) *reinterpret_cast<float4*>(a.h_out + (size_t)m * K + k) = w;
+                        w.x -= mean; w.y -= mean; w.z -= mean; w.w -= mean;
+                        ss += w.x * w.x + w.y * w.y + w.z * w.z + w.w * w.w;
                         __nv_bfloat162 o0 = __floats2bfloat162_rn(w.x * gm.x, w.y * gm.y);
                         __nv_bfloat162 o1 = __floats2bfloat162_rn(w.z * gm.z, w.w * gm.w);
                         uint2 o;
@@ -481,7 +502,11 @@ __global__ void __launch_bounds__(SG_WARPS * 32, 2) skinny_gemm_kernel(const Ski
             for (int e = 0; e < 2; ++e) {
                 const int tok = nt * 8 + 2 * t + e;
                 if (tok >= a.M) continue;
-                const float lo = c[0][nt][e] * inv_tok[nt][e], hi = c[0][nt][2 + e] * inv_tok[nt][e];
+                float lo = c[0][nt][e] * inv_tok[nt][e], hi = c[0][nt][2 + e] * inv_tok[nt][e];
+                if (NORM && a.beta_dot) {
+                    if (row_lo >= 0) lo += a.beta_dot[row_lo];
+                    if (row_hi >= 0) hi += a.beta_dot[row_hi];
+                }
                 if (EPI == EPI_SWIGLU) {
                     if (row_lo >= 0) {
                         float gt = lo, up = hi, slope = 1.f;
@@ -857,7 +882,8 @@ static int skinny_run(SkinnyArgs& a, int epilogue, cudaStream_t stream) {
 // 2 SwiGLU on W = gate|up stacked, y bfloat16 [M, O/2].
 static int skinny_gemm_run(void* y, const void* W, const void* x, const float* h, const void* delta,
                            const float* gamma, const int* row_idx, float* h_out, float eps, int M, int O, int K,
-                           int epilogue, float glu_limit, float glu_slope, cudaStream_t stream) {
+                           int epilogue, float glu_limit, float glu_slope, cudaStream_t stream, int center = 0,
+                           const float* beta_dot = nullptr) {
     if (epilogue == EPI_CONV || !zai_skinny_gemm_supports(M, O, K, epilogue, h != nullptr)) return ZAI_BAD_SIZE;
     const int cs = (!h && (epilogue == EPI_BF16 || epilogue == EPI_F32)) ? splitk_cluster(K) : 0;
     if (cs) {
@@ -876,6 +902,8 @@ static int skinny_gemm_run(void* y, const void* W, const void* x, const float* h
     a.F = O / 2;
     a.glu_limit = glu_limit;
     a.glu_slope = glu_slope;
+    a.center = center;
+    a.beta_dot = beta_dot;
     a.ldy = epilogue == EPI_SWIGLU ? O / 2 : O;
     if (epilogue == EPI_SWIGLU) {
         skinny_plan(a.F * 2, false, K, &a.n_tiles, &a.half_tiles, &a.tpc, &a.sk, &a.units);   // 8 gate + 8 up rows per tile
@@ -889,6 +917,16 @@ ZAI_API int zai_skinny_gemm(void* y, const void* W, const void* x, const float* 
                             const float* gamma, const int* row_idx, float* h_out, float eps, int M, int O, int K,
                             int epilogue, cudaStream_t stream) {
     return skinny_gemm_run(y, W, x, h, delta, gamma, row_idx, h_out, eps, M, O, K, epilogue, 0.f, 1.f, stream);
+}
+
+// The product behind a layer norm: x = (v - mean(v)) * rsqrt(mean((v - mean(v))^2) + eps) * gamma + beta with
+// v = h[row_idx] + delta[row_idx], the norm's bias carried as beta_dot = W . beta [O] (32-bit).  epilogue 0, 1 or 2; with
+// epilogue 2 and limit > 0 the gated epilogue with bounded branches.
+ZAI_API int zai_skinny_gemm_layernorm(void* y, const void* W, const float* h, const void* delta, const float* gamma,
+                                      const float* beta_dot, const int* row_idx, float* h_out, float eps, int M, int O, int K,
+                                      int epilogue, float limit, float slope, cudaStream_t stream) {
+    if (!h || !gamma || !beta_dot || epilogue == EPI_CONV) return ZAI_BAD_SIZE;
+    return skinny_gemm_run(y, W, nullptr, h, delta, gamma, row_idx, h_out, eps, M, O, K, epilogue, limit, slope, stream, 1, beta_dot);
 }
 
 // The gated epilogue with bounded branches on W = gate|up stacked, y bfloat16 [M, O/2]:

@@ -51,6 +51,8 @@ class Engine:
         self.config = self.runner.config
         self.scheduler = Scheduler(self.runner.cache, max_num_seqs, max_batched_tokens, self.max_model_len,
                                    owner=self.runner)
+        if hasattr(self.runner.ops, "require") and self.runner.device.type == "cuda":
+            self.runner.ops.require(self.runner.dtype, ("sampling",))         # the step function alone (trace replay) does not sample
         self.sampler = Sampler(self.runner.ops, self.runner.device)
         self._next_id = 0
         self.pipeline = bool(pipeline) and not profile

@@ -86,6 +86,7 @@ _SIGNATURES = {
         "zai_skinny_gemm_supports": [_I, _I, _I, _I, _I],
         "zai_skinny_gemm": [_P, _P, _P, _P, _P, _P, _P, _P, _F, _I, _I, _I, _I, _P],
         "zai_skinny_gemm_clamped_glu": [_P, _P, _P, _P, _P, _P, _P, _P, _F, _I, _I, _I, _F, _F, _P],
+        "zai_skinny_gemm_layernorm": [_P, _P, _P, _P, _P, _P, _P, _P, _F, _I, _I, _I, _I, _F, _F, _P],
         "zai_skinny_conv": [_P, _P, _P, _P, _P, _P, _P, _F, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
         "zai_skinny_hint_next": [_P, ctypes.c_longlong],
     },
@@ -157,8 +158,9 @@ def _check(code: int, what: str, n: int = 1) -> None:
     raise KernelError(f"{what}: CUDA error {code} at launch")
 
 
-CORE_LIBS = ("embed", "norm", "activation", "shortconv", "rope_kv", "attention", "sampling")
+CORE_LIBS = ("embed", "norm", "activation", "rope_kv", "attention")
 BF16_LIBS = ("attention_mma", "attention_tma", "attention_tc", "decode_gemm")
+BF16_ONLY = ("gemm_tc", "gemm_tc_pair", "stream_gemm")       # libraries that a part may name and only a bfloat16 model uses
 
 
 def require(dtype=None, extra=()) -> None:
@@ -168,15 +170,19 @@ def require(dtype=None, extra=()) -> None:
     further libraries that the model's parts name (`kernel_libs`)."""
     if not torch.cuda.is_available():
         raise KernelError("no CUDA device: this engine has no CPU path")
-    libs = list(CORE_LIBS) + [x for x in extra if x not in CORE_LIBS]
-    if dtype is None or dtype == torch.bfloat16:
+    bf16 = dtype is None or dtype == torch.bfloat16
+    libs = list(CORE_LIBS) + [x for x in extra if x not in CORE_LIBS and (bf16 or x not in BF16_ONLY)]
+    if dtype is None:
+        libs += ["shortconv", "sampling"]
+    if bf16:
         libs += list(BF16_LIBS)
         if dtype is None or USE_TC_GEMM:
             libs.append("gemm_tc")
-        if dtype is None or USE_PAIR_GEMM:
+        if dtype is None:
             libs.append("gemm_tc_pair")
         if dtype is None or USE_STREAM_GEMM:
             libs.append("stream_gemm")
+    libs = list(dict.fromkeys(libs))
     build.build_some(libs, verbose=True)
     for lib in libs:
         build.load(lib)
@@ -332,6 +338,7 @@ def _product_class(x, w, epilogue, *rest, **kw):
 
 # ----------------------------------------------------------------------------- kernels
 fuses_norm = True       # `linear` and `linear_swiglu` take a LazyNorm and apply it inside the product kernel
+fuses_layernorm = True  # ... also one that is a layer norm (`LazyNorm.beta`)
 
 _EPI_BF16, _EPI_F32, _EPI_SWIGLU = 0, 1, 2
 
@@ -408,6 +415,25 @@ def _hint_next_weights(w) -> None:
         _fn("decode_gemm", "zai_skinny_hint_next")(nxt.data_ptr(), nxt.numel() * nxt.element_size())
 
 
+_through = {}           # (weights, bias) by address -> (weak reference to the weights, W . beta in 32-bit)
+
+
+def _bias_through(w, beta):
+    """W . beta [O] in 32-bit: what a layer norm's bias contributes to every row of the product behind it.  Made the first
+    time a pair is met (steps run kernel by kernel before any graph is captured) and kept while the weights live."""
+    key = (w.data_ptr(), beta.data_ptr())
+    hit = _through.get(key)
+    if hit is not None and hit[0]() is w:
+        return hit[1]
+    if len(_through) > 4096:
+        _through.clear()
+    if torch.backends.cuda.matmul.allow_tf32:
+        torch.backends.cuda.matmul.allow_tf32 = False
+    v = torch.mv(w.float(), beta.float()).contiguous()
+    _through[key] = (weakref.ref(w), v)
+    return v
+
+
 @_timed(_product_class)
 def _skinny(x, w, epilogue, out_cols, out_dtype, glu=None):
     """The few-rows product kernel, if it takes these operands; else None.  `glu` = (limit, slope): the gated epilogue
@@ -431,8 +457,15 @@ def _skinny(x, w, epilogue, out_cols, out_dtype, glu=None):
         res = x.residual
         _cuda(res.data, x.delta, x.gamma, x.rows)
         h_out = torch.empty_like(res.data) if (x.rows is None and x.delta is not None) else None
-        _check(fn(_ptr(y), _ptr(w), None, _ptr(res.data), _ptr(x.delta), _ptr(x.gamma), _ptr(x.rows), _ptr(h_out),
-                  float(x.eps), M, O, K, *tail), "skinny_gemm")
+        if getattr(x, "beta", None) is not None:
+            # a layer norm: the kernel takes the mean off; the norm's bias goes through the product once per matrix
+            limit, slope = (float(glu[0]), float(glu[1])) if glu is not None else (0.0, 1.0)
+            _check(_fn("decode_gemm", "zai_skinny_gemm_layernorm")(
+                _ptr(y), _ptr(w), _ptr(res.data), _ptr(x.delta), _ptr(x.gamma), _ptr(_bias_through(w, x.beta)), _ptr(x.rows),
+                _ptr(h_out), float(x.eps), M, O, K, epilogue, limit, slope, _stream()), "skinny_gemm")
+        else:
+            _check(fn(_ptr(y), _ptr(w), None, _ptr(res.data), _ptr(x.delta), _ptr(x.gamma), _ptr(x.rows), _ptr(h_out),
+                      float(x.eps), M, O, K, *tail), "skinny_gemm")
         if h_out is not None:
             res.data = h_out
     else:

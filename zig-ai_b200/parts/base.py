@@ -147,23 +147,29 @@ class NormedTerm:
 
 
 class LazyNorm:
-    """A norm that has not run yet: `norm(residual + delta) * gamma`, optionally on gathered rows.
-    A product kernel that can apply it on the fly takes it as its input (`ops.linear`,
-    `ops.linear_swiglu`); anything else calls `materialize`."""
+    """A norm that has not run yet: `norm(residual + delta) * gamma`, optionally on gathered rows; with `beta` a
+    layer norm (the mean taken off, `beta` added), else an RMS norm.  A product kernel that can apply it on the fly
+    takes it as its input (`ops.linear`, `ops.linear_swiglu`, `ops.linear_clamped_glu`); anything else calls
+    `materialize`."""
 
-    def __init__(self, residual: Residual, delta, gamma, eps: float, dtype, rows=None):
+    def __init__(self, residual: Residual, delta, gamma, eps: float, dtype, rows=None, beta=None):
         self.residual, self.delta, self.gamma, self.eps, self.dtype, self.rows = residual, delta, gamma, eps, dtype, rows
+        self.beta = beta
 
     @property
     def shape(self):
         n = self.rows.numel() if self.rows is not None else self.residual.data.shape[0]
         return (n, self.residual.data.shape[1])
 
+    def _norm(self, ops, h, delta):
+        if self.beta is not None:
+            return ops.add_layernorm(h, delta, self.gamma, self.beta, self.eps, self.dtype)
+        return ops.add_rmsnorm(h, delta, self.gamma, self.eps, self.dtype)
+
     def materialize(self, ops):
         if self.rows is not None:
-            h = ops.gather_add(self.residual.data, self.delta, self.rows)
-            return ops.add_rmsnorm(h, None, self.gamma, self.eps, self.dtype)
-        return ops.add_rmsnorm(self.residual.data, self.delta, self.gamma, self.eps, self.dtype)
+            return self._norm(ops, ops.gather_add(self.residual.data, self.delta, self.rows), None)
+        return self._norm(ops, self.residual.data, self.delta)
 
 
 # --------------------------------------------------------------------------- interfaces

@@ -13,6 +13,7 @@ from .base import FeedForward, ParamDecl, register_part
 class SwiGlu(FeedForward):
     accepts_lazy_input = True     # x goes straight into a product
     graph_safe = True      # forward launches kernels only; nothing is read back to the host
+    kernel_libs = ("gemm_tc_pair",)       # gate/up products of many rows with the activation as their epilogue (bfloat16)
 
     def __init__(self, hidden: int, ff_dim: int):
         self.hidden, self.ff_dim = int(hidden), int(ff_dim)

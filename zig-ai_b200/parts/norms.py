@@ -63,10 +63,10 @@ class LayerNorm(Norm):
         ops = step.ops
         if isinstance(delta, NormedTerm):
             raise TypeError("a layer norm takes a plain pending term")
-        if rows is not None:
-            picked = ops.gather_add(res.data, delta, rows)
-            return ops.add_layernorm(picked, None, self.weight, self.bias, self.eps, self.dtype)
-        return ops.add_layernorm(res.data, delta, self.weight, self.bias, self.eps, self.dtype)
+        x = LazyNorm(res, delta, self.weight, self.eps, self.dtype, rows, beta=self.bias)
+        if lazy and getattr(ops, "fuses_layernorm", False):
+            return x                         # a product kernel applies it (steps of few rows)
+        return x.materialize(ops)
 
 
 register_part("norm", "rmsnorm", RmsNorm)

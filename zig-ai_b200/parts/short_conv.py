@@ -24,6 +24,7 @@ MAX_TAPS = 16      # ZAI_MAX_TAPS of csrc/shortconv.cu
 class ShortConv(Mixer):
     accepts_lazy_input = True     # x goes straight into a product
     graph_safe = True      # forward launches kernels only; nothing is read back to the host
+    kernel_libs = ("shortconv",)
 
     def __init__(self, hidden: int, conv_dim: int, taps: int, bias: bool):
         self.hidden, self.conv_dim, self.taps, self.bias = int(hidden), int(conv_dim), int(taps), bool(bias)
