@@ -62,11 +62,11 @@ ONLY = {
 
 # head sizes and widths that the tensor-core attention kernels and the few-rows product kernels take, for the
 # whole-model GPU tests in bfloat16
-P_C = config(1000, 256, 1e-6, 0.5, 30.0, [
-    attention(4, 2, 64, 64, 0.125, 32, 1000000.0, mask=96, ff=384, limit=1.0),
-    latent(4, 32, 32, 64, 128, 0.1, 10000.0, scaling=(8.0, 128.0, 16.0, 1.0), ff=256, limit=2.0),
+P_C = config(1000, 320, 1e-6, 0.7, 30.0, [
+    attention(4, 2, 64, 64, 0.125, 32, 1000000.0, mask=96, ff=512, limit=1.5),
+    latent(4, 48, 32, 64, 160, 0.1, 10000.0, scaling=(4.0, 128.0, 16.0, 1.0), ff=256, limit=2.0),
     attention(8, 1, 128, 64, 0.09, 64, 10000.0, mask=160),
-    latent(8, 16, 32, 48, 128, 0.15, 10000.0, scaling=(8.0, 128.0, 16.0, 1.0), kv_from=1, ff=384, limit=1.0),
+    latent(8, 16, 32, 48, 160, 0.15, 10000.0, scaling=(4.0, 128.0, 16.0, 1.0), kv_from=1, ff=448, limit=1.0),
 ])
 
 ALL = {"A": (P_A, 31), "B": (P_B, 37), "C": (P_C, 41)}

@@ -52,7 +52,7 @@ def test_add_layernorm(dtype, N, H, eps):
 def test_rotation_table_plain_and_stretched(scaling):
     o = ops()
     step = make_step(o, torch.float32, [0, 700, 31], [9, 1, 40], 16, 128, 3)
-    for dims, theta in ((8, 10000.0), (32, 500000.0), (6, 300.0)):
+    for dims, theta in ((8, 10000.0), (32, 250000.0), (6, 300.0)):
         a = o.rope_table(step, dims, theta, torch.device("cuda"), scaling)
         b = ref_ops.rope_table(step, dims, theta, torch.device("cuda"), scaling)
         assert a.shape == (50, dims // 2, 2) and torch.allclose(a.cpu(), b.cpu(), atol=2e-7, rtol=0)
@@ -60,7 +60,7 @@ def test_rotation_table_plain_and_stretched(scaling):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H,G,D,Dv,rot,scope", [(4, 2, 16, 16, 8, 2), (3, 1, 32, 8, 32, 2), (6, 3, 24, 40, 0, 2), (2, 2, 128, 128, 64, 2),
-                                                (5, 5, 10, 6, 4, 1), (8, 2, 64, 64, 64, 0), (6, 1, 128, 64, 64, 2)])
+                                                (5, 5, 10, 6, 4, 1), (8, 2, 64, 64, 64, 0), (8, 1, 128, 64, 32, 2)])
 def test_qkv_prepare(dtype, H, G, D, Dv, rot, scope):
     """q, k and v from a wider stacked projection (a gate's columns behind them): the norm in its three scopes, the
     rotation, heads padded to the cache's size, and the rows written at the right page and offset."""
@@ -88,7 +88,7 @@ def test_qkv_prepare(dtype, H, G, D, Dv, rot, scope):
 
 
 CHUNK_SHAPES = [(4, 2, 16, 8, 11), (3, 1, 32, 8, 1), (6, 3, 48, 4, 7), (8, 2, 80, 32, 64), (16, 8, 64, 16, 96),
-                (2, 2, 128, 16, 120), (6, 1, 128, 64, 100), (5, 5, 112, 16, 5000), (2, 1, 200, 16, 33)]
+                (2, 2, 128, 16, 112), (8, 1, 128, 64, 100), (5, 5, 112, 16, 5000), (2, 1, 200, 16, 33)]
 
 
 @pytest.mark.parametrize("dtype,impl", [(torch.float32, None), (torch.bfloat16, None), (torch.bfloat16, "general")])
@@ -159,7 +159,7 @@ def latent_pages(step, ctx, q_lens, ps, W, dtype, num_pages, g):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("H,D,Dr,R", [(4, 32, 32, 128), (3, 12, 8, 24), (5, 4, 16, 40), (2, 20, 6, 17), (16, 64, 64, 256), (9, 8, 2, 300)])
+@pytest.mark.parametrize("H,D,Dr,R", [(4, 48, 32, 160), (3, 12, 8, 24), (5, 4, 16, 40), (2, 20, 6, 17), (16, 64, 64, 256), (9, 8, 2, 300)])
 def test_latent_prepare(dtype, H, D, Dr, R):
     o = ops()
     g = torch.Generator().manual_seed(7)
@@ -184,7 +184,7 @@ def test_latent_prepare(dtype, H, D, Dr, R):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("H,R,Dr,ps", [(4, 128, 32, 64), (3, 24, 8, 8), (5, 40, 16, 16), (2, 17, 6, 8), (16, 256, 64, 32), (9, 300, 2, 16),
+@pytest.mark.parametrize("H,R,Dr,ps", [(4, 160, 32, 64), (7, 128, 16, 32), (3, 24, 8, 8), (5, 40, 16, 16), (2, 17, 6, 8), (16, 256, 64, 32), (9, 300, 2, 16),
                                        (1, 512, 64, 16)])
 def test_latent_attention_spans_and_single_tokens(dtype, H, R, Dr, ps):
     o = ops()
