@@ -13,7 +13,7 @@ import torch
 import plain_pikasun as P
 import traces
 from pikasun_configs import ALL, ONLY, PAGE_SIZE
-from test_pikasun_cpu import rows_at_chunk_edges, tokens
+from test_pikasun_cpu import random_configuration, rows_at_chunk_edges, tokens
 from zig_ai_b200.config import config_from_dict
 from zig_ai_b200.weights import write_random_model
 
@@ -140,6 +140,24 @@ def test_sharp_latent_attention_over_far_rows_and_page_borders(models, dtype):
             assert np.abs(rows - want).max() < 2e-3, rid
         else:
             traces.check_request(rows, want, dtype, f"sharp latent, cut {rid}", bf16_row=0.35, bf16_mean=0.12)
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_configurations(tmp_path, seed):
+    """Configurations drawn at random (small sizes that are no multiple of anything a kernel likes) in 32-bit: whole,
+    in portions that repeat often enough for the step graphs, and with a decoded tail."""
+    from zig_ai_b200.engine.runner import load_runner
+    g = random.Random(2000 + seed)
+    cfg = random_configuration(g)
+    d = str(tmp_path / "m")
+    write_random_model(config_from_dict(cfg), seed, d, matrix_std="fan_in")
+    c, W = P.read_config(d), P.read_weights(d)
+    toks = tokens(cfg["vocab"], 150, seed)
+    want = P.forward(c, W, toks).numpy()
+    r = load_runner(d, "float32", max_tokens=256, max_requests=4, page_size=g.choice([8, 16, 64]))
+    got = run_cuts(r, toks, {"w": [150], "p": [9, 2, 17, 1, 1, 3, 30, 2, 5] * 2 + [10], "d": [110] + [1] * 40})
+    for rid, rows in got.items():
+        traces.check_request(rows, want, "float32", f"random configuration {seed}, cut {rid}")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

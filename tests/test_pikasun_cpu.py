@@ -286,3 +286,52 @@ def test_tensors_are_named_and_shaped_by_the_configuration(models):
     assert decls["l2.mlp.gate"].shape == (72, 66) and decls["l2.norm2.b"].shape == (66,)
     stored = set(SafetensorsFile(f"{models['B']}/model.safetensors").names())
     assert stored == set(decls)
+
+
+def random_configuration(g):
+    """A small Pikasun configuration drawn at random: layer kinds and order, head counts, head sizes that differ between
+    q/k and v, ranks and rotated parts, chunk sizes from one position to longer than the prompt, plain and stretched
+    rotations, layers that borrow an earlier layer's latent, layers without feed-forward, logits with and without a cap."""
+    from pikasun_configs import attention, config, latent
+    layers, own = [], []
+    for i in range(g.randint(2, 6)):
+        ff = None if g.random() < 0.25 else g.choice([24, 56, 100])
+        limit = g.choice([0.5, 1.0, 3.0])
+        if g.random() < 0.4:
+            heads = g.choice([1, 2, 3, 4, 6])
+            kv = g.choice([k for k in (1, 2, 3, 4, 6) if heads % k == 0])
+            dim = g.choice([4, 8, 12, 16, 24])
+            rot = g.choice([dim, dim // 4 * 2, 0])
+            layers.append(attention(heads, kv, dim, g.choice([dim, 4, 8, 20]), g.choice([dim ** -0.5, 0.2, 0.45]), rot,
+                                    g.choice([300.0, 10000.0, 1e6]), mask=g.choice([None, 1, 2, 5, 9, 16, 31, 200]), ff=ff, limit=limit))
+        else:
+            heads, dim, vdim = g.choice([1, 2, 3, 5]), g.choice([4, 6, 16]), g.choice([4, 10, 16])
+            src = g.choice(own) if own and g.random() < 0.4 else None
+            if src is None:
+                rot_dim, rank, base = g.choice([2, 4, 8, 12]), g.choice([8, 17, 24, 32]), g.choice([300.0, 10000.0])
+                scaling = g.choice([None, (4.0, 32.0, 8.0, 1.0), (16.0, 24.0, 4.0, 0.5), (2.0, 1000.0, 2.0, 1.0)])
+                own.append(i)
+            else:
+                m = layers[src]["mixer"]
+                rot_dim, rank, base = m["rot_dim"], m["kv_rank"], m["rot"]["base"]
+                sc = m["rot"].get("scaling")
+                scaling = None if sc is None else tuple(sc[k] for k in ("factor", "original", "fast", "slow"))
+            layers.append(latent(heads, dim, rot_dim, vdim, rank, g.choice([0.2, (dim + rot_dim) ** -0.5]), base, scaling=scaling,
+                                 kv_from=src, ff=ff, limit=limit))
+    return config(g.choice([61, 97, 130]), g.choice([24, 40, 50, 64]), g.choice([1e-5, 1e-6]), g.choice([0.5, 1.0, 1.7]),
+                  g.choice([None, 4.0, 30.0]), layers)
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_random_configurations(tmp_path, seed):
+    g = random.Random(1000 + seed)
+    cfg = random_configuration(g)
+    d = str(tmp_path / "m")
+    write_random_model(config_from_dict(cfg), seed, d, matrix_std="fan_in")
+    toks = tokens(cfg["vocab"], 70, seed)
+    want = plain(d, toks)
+    r = runner(d, g.choice([4, 8, 16]), max_tokens=128)
+    close(run_cut(r, "w", toks, [70]), want, "whole")
+    close(run_cut(r, "p", toks, [9, 2, 17, 1, 1, 3, 30, 2, 5]), want, "portions")
+    close(run_cut(r, "d", toks, [50] + [1] * 20), want, "decoded tail")
+    r.cache.check()
