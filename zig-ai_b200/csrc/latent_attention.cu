@@ -335,32 +335,39 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(
 // requests, or single tokens of several requests) take their turns one after the other.
 template <int LM_COLS>
 __global__ void __launch_bounds__(128) latent_attention_rows_kernel(
-    bf16* __restrict__ out, const bf16* __restrict__ q_lat, const bf16* __restrict__ q_rot, const bf16* __restrict__ pages,
-    const int* __restrict__ block_table, int table_width, const int* __restrict__ positions, const int* __restrict__ seq_idx,
-    int page_size, int N, int H, int R, int Dr, float scale_log2, int num_pages, int* __restrict__ status) {
+    bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, const bf16* __restrict__ q_lat,
+    const bf16* __restrict__ q_rot, const bf16* __restrict__ pages, const int* __restrict__ block_table, int table_width,
+    const int* __restrict__ positions, const int* __restrict__ seq_idx, int page_size, int N, int H, int R, int Dr,
+    float scale_log2, int split_keys, int n_splits, int num_pages, int* __restrict__ status) {
     extern __shared__ __align__(16) unsigned char lm_smem[];
-    __shared__ int s_seq[4], s_kend[4];
+    __shared__ int s_key[4], s_khi[4];
     const int W = R + Dr, ST = W + 8;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int HG = (H + 15) / 16, RCH = (R + LM_COLS - 1) / LM_COLS;
     pdl_trigger();
     pdl_wait();
+    // groups of heads fastest, then blocks of columns, then ranges of keys, then rows: neighbours share their cached rows
     long long w = (long long)blockIdx.x * 4 + warp;
-    const bool live = w < (long long)N * HG * RCH;
+    const bool live = w < (long long)N * n_splits * RCH * HG;
+    const int hg = live ? (int)(w % HG) : 0;
+    w /= HG;
     const int rc = live ? (int)(w % RCH) : 0;
     w /= RCH;
-    const int hg = live ? (int)(w % HG) : 0;
-    const int t = live ? (int)(w / HG) : 0;
+    const int split = live ? (int)(w % n_splits) : 0;
+    const int t = live ? (int)(w / n_splits) : 0;
     bf16* sq = reinterpret_cast<bf16*>(lm_smem) + (size_t)warp * 16 * ST;         // [16][ST] this warp's queries
     bf16* sk = reinterpret_cast<bf16*>(lm_smem) + (size_t)4 * 16 * ST;            // 2 x [LM_KT][ST] the block's cached rows
     const int h0 = hg * 16, col0 = rc * LM_COLS;
     const int g = lane >> 2, tq = lane & 3;
-    const int my_seq = live ? seq_idx[t] : -1, my_kend = live ? positions[t] + 1 : 0;
+    const int my_kbeg = split * split_keys;
+    const int my_khi = live ? min(positions[t] + 1, my_kbeg + split_keys) : 0;
+    const bool empty = !live || my_kbeg >= my_khi;           // (a range that holds no key of the row)
+    const int my_key = empty ? -1 : seq_idx[t] * n_splits + split;               // what a group shares: the request and the range
     if (lane == 0) {
-        s_seq[warp] = my_seq;
-        s_kend[warp] = my_kend;
+        s_key[warp] = my_key;
+        s_khi[warp] = my_khi;
     }
-    if (live) {
+    if (!empty) {
         for (int idx = lane; idx < 16 * (W / 8); idx += 32) {
             const int r = idx / (W / 8), c = (idx - r * (W / 8)) * 8;
             const bool valid = h0 + r < H;
@@ -377,19 +384,20 @@ __global__ void __launch_bounds__(128) latent_attention_rows_kernel(
     const int cols = min(LM_COLS, R - col0);
     __syncthreads();
     for (int leader = 0; leader < 4; ++leader) {
-        const int seq = s_seq[leader];
-        bool first = seq >= 0;                               // (the same for every thread: all read shared memory)
-        for (int e = 0; e < leader; ++e) first = first && s_seq[e] != seq;
+        const int key = s_key[leader];
+        bool first = key >= 0;                               // (the same for every thread: all read shared memory)
+        for (int e = 0; e < leader; ++e) first = first && s_key[e] != key;
         if (!first) continue;
         int kmax = 0;
         for (int e = leader; e < 4; ++e)
-            if (s_seq[e] == seq) kmax = max(kmax, s_kend[e]);
-        const bool member = my_seq == seq;
-        const ZaiTableRow table{block_table + (size_t)seq * table_width, table_width, num_pages, status};
-        const int n_tiles = (kmax + LM_KT - 1) / LM_KT;
+            if (s_key[e] == key) kmax = max(kmax, s_khi[e]);
+        const bool member = my_key == key;
+        const int kbeg = (key % n_splits) * split_keys;
+        const ZaiTableRow table{block_table + (size_t)(key / n_splits) * table_width, table_width, num_pages, status};
+        const int n_tiles = (kmax - kbeg + LM_KT - 1) / LM_KT;
         // a tile: row tid / 4 of the 32, sixteen bytes a copy, four threads a row
         auto load = [&](int i) {
-            const int j = i * LM_KT + (tid >> 2);
+            const int j = kbeg + i * LM_KT + (tid >> 2);
             const bf16* src = j < kmax ? pages + ((size_t)table.page(j / page_size) * page_size + j % page_size) * W : nullptr;
             bf16* dst = sk + (size_t)(i & 1) * LM_KT * ST + (tid >> 2) * ST;
             for (int c = tid & 3; c < W / 8; c += 4) cp_async16(dst + c * 8, src ? src + c * 8 : pages, src != nullptr);
@@ -405,25 +413,62 @@ __global__ void __launch_bounds__(128) latent_attention_rows_kernel(
                 cp_async_wait<0>();
             }
             __syncthreads();
-            if (member && i * LM_KT < my_kend)
-                lm_tile<LM_COLS>(o, m0, m1, l0, l1, sq, sk + (size_t)(i & 1) * LM_KT * ST, ST, W, i * LM_KT, my_kend, col0, cols,
+            if (member && kbeg + i * LM_KT < my_khi)
+                lm_tile<LM_COLS>(o, m0, m1, l0, l1, sq, sk + (size_t)(i & 1) * LM_KT * ST, ST, W, kbeg + i * LM_KT, my_khi, col0, cols,
                                  scale_log2, lane);
             __syncthreads();                                 // the buffer is loaded again two tiles on
         }
     }
     if (!live) return;
+    const int ha = h0 + g, hb = ha + 8;
+    if (empty) {                                             // (only with several ranges)
+        if (rc == 0 && tq == 0) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int h = e ? hb : ha;
+                if (h < H) {
+                    float* ml = part_ml + (((size_t)t * H + h) * n_splits + split) * 2;
+                    ml[0] = -INFINITY;
+                    ml[1] = 0.f;
+                }
+            }
+        }
+        return;
+    }
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-    const int ha = h0 + g, hb = ha + 8;
-    const float inv0 = 1.f / l0, inv1 = 1.f / l1;
+    if (n_splits == 1) {
+        const float inv0 = 1.f / l0, inv1 = 1.f / l1;
+#pragma unroll
+        for (int j = 0; j < LM_COLS / 8; ++j) {
+            const int d = j * 8 + 2 * tq;
+            if (d < cols) {
+                if (ha < H) *reinterpret_cast<uint32_t*>(out + ((size_t)t * H + ha) * R + col0 + d) = pack_bf16(o[j][0] * inv0, o[j][1] * inv0);
+                if (hb < H) *reinterpret_cast<uint32_t*>(out + ((size_t)t * H + hb) * R + col0 + d) = pack_bf16(o[j][2] * inv1, o[j][3] * inv1);
+            }
+        }
+        return;
+    }
 #pragma unroll
     for (int j = 0; j < LM_COLS / 8; ++j) {
         const int d = j * 8 + 2 * tq;
         if (d < cols) {
-            if (ha < H) *reinterpret_cast<uint32_t*>(out + ((size_t)t * H + ha) * R + col0 + d) = pack_bf16(o[j][0] * inv0, o[j][1] * inv0);
-            if (hb < H) *reinterpret_cast<uint32_t*>(out + ((size_t)t * H + hb) * R + col0 + d) = pack_bf16(o[j][2] * inv1, o[j][3] * inv1);
+            if (ha < H) *reinterpret_cast<float2*>(part_o + (((size_t)t * H + ha) * n_splits + split) * R + col0 + d) = make_float2(o[j][0], o[j][1]);
+            if (hb < H) *reinterpret_cast<float2*>(part_o + (((size_t)t * H + hb) * n_splits + split) * R + col0 + d) = make_float2(o[j][2], o[j][3]);
+        }
+    }
+    if (rc == 0 && tq == 0) {
+        if (ha < H) {
+            float* ml = part_ml + (((size_t)t * H + ha) * n_splits + split) * 2;
+            ml[0] = m0 * scale_log2;
+            ml[1] = l0;
+        }
+        if (hb < H) {
+            float* ml = part_ml + (((size_t)t * H + hb) * n_splits + split) * 2;
+            ml[0] = m1 * scale_log2;
+            ml[1] = l1;
         }
     }
 }
@@ -463,10 +508,12 @@ ZAI_API int zai_latent_attention_mma(void* out, float* part_o, float* part_ml, c
     if (N <= 0) return ZAI_OK;
     if (!zai_latent_attention_mma_supports(R, Dr) || H < 1 || n_splits < 1 || split_keys < LM_KT || split_keys % LM_KT) return ZAI_BAD_SIZE;
     const int cols = R <= 128 ? 128 : 256;
-    if (n_splits == 1) {
-        // many rows: four warps a block share the tiles
+    const int sharers = ((H + 15) / 16) * ((R + cols - 1) / cols);      // warps that read the same cached rows
+    if (n_splits == 1 || (sharers >= 2 && (long long)N * sharers * n_splits >= 1024)) {
+        // many rows, or several groups of heads (blocks of columns) a row and warps enough to fill the device although a
+        // block's groups take turns: four warps a block share the tiles
         const size_t smem = (size_t)(4 * 16 + 2 * LM_KT) * (R + Dr + 8) * 2;
-        const long long warps = (long long)N * ((H + 15) / 16) * ((R + cols - 1) / cols);
+        const long long warps = (long long)N * sharers * n_splits;
         const long long blocks = (warps + 3) / 4;
         if (blocks > 0x7fffffffLL || smem > 200 * 1024) return ZAI_BAD_SIZE;
         static unsigned long long done_rows = 0;
@@ -475,9 +522,12 @@ ZAI_API int zai_latent_attention_mma(void* out, float* part_o, float* part_ml, c
             cudaFuncSetAttribute(latent_attention_rows_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         }
         auto rows_kernel = cols == 128 ? latent_attention_rows_kernel<128> : latent_attention_rows_kernel<256>;
-        return launch_pdl(rows_kernel, dim3((unsigned)blocks), dim3(128), smem, stream, (bf16*)out, (const bf16*)q_lat,
-                          (const bf16*)q_rot, (const bf16*)pages, block_table, table_width, positions, seq_idx, page_size, N, H, R, Dr,
-                          scale * 1.4426950408889634f, num_pages, status);
+        int rc = launch_pdl(rows_kernel, dim3((unsigned)blocks), dim3(128), smem, stream, (bf16*)out, part_o, part_ml,
+                            (const bf16*)q_lat, (const bf16*)q_rot, (const bf16*)pages, block_table, table_width, positions, seq_idx,
+                            page_size, N, H, R, Dr, scale * 1.4426950408889634f, split_keys, n_splits, num_pages, status);
+        if (rc != 0 || n_splits == 1) return rc;
+        return launch_pdl(latent_combine_kernel, dim3((unsigned)((size_t)N * H)), dim3(128), 0, stream, (bf16*)out,
+                          (const float*)part_o, (const float*)part_ml, R, n_splits);
     }
     const size_t per_warp = (size_t)(16 + 2 * LM_KT) * (R + Dr + 8) * 2;
     int wpb = (int)((200 * 1024) / per_warp);
